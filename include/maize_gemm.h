@@ -1,0 +1,159 @@
+/*
+ * maize_gemm.h - C ABI of the B200-native BF16 GEMM that stands in for the one
+ * hot path of averyparr/maize: the pipelined tiled BF16 GEMM its demo traces.
+ *
+ * The reference has no runtime boundary for this path (it prints PTX), so each
+ * entry point cites the reference interface whose role it takes over:
+ *
+ *   - the kernel argument list (A ptr, a_rows, a_cols, B ptr, b_rows, b_cols)
+ *     of the traced GEMM kernel                             src/main.rs:32-39
+ *   - the {ptr, nrows, ncols} argument bundle GlobalMatrix  src/main.rs:20-27
+ *     and maize_tile::gmem::Matrix      crates/maize_tile/src/gmem/matrix.rs:13-18
+ *   - the per-tile GEMM entry point sm80_gemm_smem_multibuffer
+ *                                       crates/maize_tile/src/gemm/mod.rs:37-90
+ *
+ * Data contract (all entry points): bf16 operands, fp32 accumulation starting at
+ * zero, one round-to-nearest-even conversion to bf16 on output.
+ *   A : M x K, row-major                     (a_rows = M, a_cols = K)
+ *   B : N x K, row-major, i.e. K-major       (b_rows = N, b_cols = K)
+ *   C : M x N, row-major,  C = A * B^T       (c_rows = M, c_cols = N)
+ * Ragged M, N and K are handled (the reference drops ragged panels,
+ * src/main.rs:56-57).  Requirements of the TMA loads: K % 8 == 0 (16-byte row
+ * pitch), A and B base addresses 16-byte aligned; otherwise
+ * MAIZE_ERR_UNSUPPORTED is returned and nothing is launched.  C needs only
+ * 2-byte alignment and any N.
+ *
+ * Every call enqueues work on the caller's CUDA stream and returns without
+ * synchronising; no call allocates device memory except maize_ctx_create and
+ * the *_host entry point (which grows a cached staging area on first use).
+ * Nothing here ever traps or asserts on the device: a device wait that runs
+ * out of its time budget records MAIZE_ERR_TIMEOUT in a status word that
+ * maize_ctx_poll reads back.
+ *
+ * Plain C: no CUDA or torch types appear in any signature; streams travel as
+ * void* (a cudaStream_t / CUstream value, NULL = the legacy default stream).
+ */
+#ifndef MAIZE_GEMM_H
+#define MAIZE_GEMM_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define MAIZE_API __attribute__((visibility("default")))
+#else
+#define MAIZE_API
+#endif
+
+typedef enum maize_status {
+    MAIZE_OK = 0,
+    MAIZE_ERR_INVALID_ARG = 1,  /* null pointer, mismatched shapes, bad leading dimension */
+    MAIZE_ERR_UNSUPPORTED = 2,  /* K % 8 != 0, misaligned A/B, dimension beyond the kernel's range */
+    MAIZE_ERR_CUDA = 3,         /* a CUDA runtime/driver call failed; see maize_last_error */
+    MAIZE_ERR_TIMEOUT = 4,      /* a bounded device wait expired (reported by maize_ctx_poll) */
+    MAIZE_ERR_DEVICE_ABORT = 5, /* the kernel saw an inconsistent state and returned early */
+    MAIZE_ERR_NO_DEVICE = 6     /* no usable CUDA device / driver */
+} maize_status_t;
+
+/* {ptr, nrows, ncols}: mirrors GlobalMatrix<T> (src/main.rs:20-27), 16 bytes, 16-byte aligned. */
+typedef struct
+#if defined(__GNUC__)
+    __attribute__((aligned(16)))
+#endif
+    maize_global_matrix {
+    void *ptr;      /* device pointer to bf16 elements, row-major, dense rows */
+    uint32_t nrows;
+    uint32_t ncols;
+} maize_global_matrix_t;
+
+typedef struct maize_ctx maize_ctx_t;
+
+/* Library version, major * 10000 + minor * 100 + patch. */
+MAIZE_API int maize_version(void);
+
+/* Static text for a status code. */
+MAIZE_API const char *maize_status_string(maize_status_t status);
+
+/*
+ * One context per host thread / stream.  Binds to `device`, queries its SM
+ * count, and allocates the small device-side state the kernels need (status
+ * word, split-K scratch).  Takes the role of the per-thread kernel builder of
+ * the reference (crates/maize_core/src/codegen/mod.rs:21-26, 50-51).
+ */
+MAIZE_API maize_status_t maize_ctx_create(int device, maize_ctx_t **out);
+MAIZE_API void maize_ctx_destroy(maize_ctx_t *ctx);
+
+/* Last error text of this context ("" if none); valid until the next call on ctx. */
+MAIZE_API const char *maize_last_error(const maize_ctx_t *ctx);
+
+/*
+ * C = A * B^T on device buffers; argument order follows the traced kernel's
+ * (ptr, rows, cols) triples (src/main.rs:32-39) plus the C triple that the
+ * reference never stores (src/main.rs:71).  Requires a_cols == b_cols,
+ * c_rows == a_rows, c_cols == b_rows.  M == 0 or N == 0 is a no-op.
+ */
+MAIZE_API maize_status_t maize_gemm_bf16(maize_ctx_t *ctx, const void *a, uint32_t a_rows, uint32_t a_cols,
+                                         const void *b, uint32_t b_rows, uint32_t b_cols, void *c, uint32_t c_rows,
+                                         uint32_t c_cols, void *cuda_stream);
+
+/* Same through the {ptr, nrows, ncols} bundles (src/main.rs:20-27). */
+MAIZE_API maize_status_t maize_gemm_bf16_m(maize_ctx_t *ctx, const maize_global_matrix_t *a,
+                                           const maize_global_matrix_t *b, const maize_global_matrix_t *c,
+                                           void *cuda_stream);
+
+/*
+ * Same with explicit leading dimensions in elements (row pitch of A, B and C):
+ * the stride_per_row of the reference's panels
+ * (crates/maize_tile/src/gmem/col_panel.rs:88-124, row_panel.rs:85-127).
+ * lda and ldb must be multiples of 8; ldc is free.  Used for row slabs of A/C
+ * and column slices of C in the N-sharded multi-GPU path.
+ */
+MAIZE_API maize_status_t maize_gemm_bf16_ld(maize_ctx_t *ctx, const void *a, uint64_t lda, const void *b,
+                                            uint64_t ldb, void *c, uint64_t ldc, uint32_t m, uint32_t n, uint32_t k,
+                                            void *cuda_stream);
+
+/*
+ * End-to-end form with HOST buffers (pinned or pageable): copies A and B to the
+ * device, runs the GEMM, copies C back, all on `cuda_stream`, and waits for the
+ * result.  Device staging is cached in the context and grows on demand.
+ * Stands where a host caller of the traced kernel (src/main.rs:31-90) would.
+ */
+MAIZE_API maize_status_t maize_gemm_bf16_host(maize_ctx_t *ctx, const void *a_host, uint32_t a_rows, uint32_t a_cols,
+                                              const void *b_host, uint32_t b_rows, uint32_t b_cols, void *c_host,
+                                              uint32_t c_rows, uint32_t c_cols, void *cuda_stream);
+
+/*
+ * Synchronises `cuda_stream`, reads and clears the device status word.
+ * MAIZE_OK, MAIZE_ERR_TIMEOUT or MAIZE_ERR_DEVICE_ABORT; replaces the
+ * reference's device-side trap (src/main.rs:54,71).
+ */
+MAIZE_API maize_status_t maize_ctx_poll(maize_ctx_t *ctx, void *cuda_stream);
+
+/* Tunables.  Keys: "timeout_ns" (device wait budget), "force_kernel" (0 = heuristic,
+ * see maize_kernel_name), "max_ctas" (cap on the persistent grid, 0 = SM count). */
+MAIZE_API maize_status_t maize_ctx_set(maize_ctx_t *ctx, const char *key, int64_t value);
+MAIZE_API maize_status_t maize_ctx_get(const maize_ctx_t *ctx, const char *key, int64_t *value);
+
+/* Name of kernel variant `id` (1-based), NULL past the end; id of the variant the
+ * heuristic picks for a shape. */
+MAIZE_API const char *maize_kernel_name(int id);
+MAIZE_API int maize_pick_kernel(const maize_ctx_t *ctx, uint32_t m, uint32_t n, uint32_t k);
+
+/* Number of kernels this context has launched since creation. */
+MAIZE_API uint64_t maize_ctx_launch_count(const maize_ctx_t *ctx);
+
+/*
+ * Self-test of the bounded-wait machinery: launches one CTA that waits on a
+ * barrier nothing will ever complete, with a budget of `budget_ns`.  The kernel
+ * returns by itself; the following maize_ctx_poll reports MAIZE_ERR_TIMEOUT.
+ */
+MAIZE_API maize_status_t maize_debug_wait_expires(maize_ctx_t *ctx, uint64_t budget_ns, void *cuda_stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MAIZE_GEMM_H */

@@ -1,0 +1,483 @@
+// C ABI of the B200 BF16 GEMM (declared in include/maize_gemm.h): argument
+// validation, TMA tensor-map construction, kernel selection and launch.
+//
+// The reference reaches its GEMM through a trace-time builder and a six-scalar
+// kernel argument list (src/main.rs:31-48); this file is the run-time boundary
+// that stands in for it.  Nothing here falls back to the CPU: without a CUDA
+// device every compute entry point returns an error.
+#include "../../include/maize_gemm.h"
+
+#include <cuda_runtime.h>
+
+#include <cstdio>
+#include <cstring>
+#include <string>
+
+#include "gemm_sm100.cuh"
+
+namespace {
+
+using maize::DeviceStatus;
+using maize::GemmParams;
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+struct KernelVariant {
+    const char *name;
+    uint32_t block_n;
+    uint32_t stages;
+};
+
+// Index + 1 is the public kernel id.
+const KernelVariant kVariants[] = {
+    {"sm100_1cta_128x256x64_s4", 256, 4},
+    {"sm100_1cta_128x128x64_s6", 128, 6},
+    {"sm100_1cta_128x64x64_s8", 64, 8},
+    {"sm100_1cta_128x32x64_s8", 32, 8},
+};
+constexpr int kNumVariants = static_cast<int>(sizeof(kVariants) / sizeof(kVariants[0]));
+
+class DeviceGuard {
+public:
+    explicit DeviceGuard(int device) : prev_(-1), changed_(false)
+    {
+        if (cudaGetDevice(&prev_) == cudaSuccess && prev_ != device) {
+            changed_ = cudaSetDevice(device) == cudaSuccess;
+        }
+    }
+    ~DeviceGuard()
+    {
+        if (changed_)
+            cudaSetDevice(prev_);
+    }
+
+private:
+    int prev_;
+    bool changed_;
+};
+
+}  // namespace
+
+struct maize_ctx {
+    int device = 0;
+    int sm_count = 0;
+    DeviceStatus *d_status = nullptr;
+    DeviceStatus *h_status = nullptr;  // pinned
+    uint64_t timeout_ns = 2000000000ull;
+    int force_kernel = 0;
+    int max_ctas = 0;
+    uint64_t launches = 0;
+    EncodeTiledFn encode = nullptr;
+    void *staging = nullptr;  // device staging for the *_host entry point
+    size_t staging_bytes = 0;
+    bool attr_set[kNumVariants] = {};
+    std::string err;
+};
+
+namespace {
+
+maize_status_t fail(maize_ctx_t *ctx, maize_status_t st, const std::string &msg)
+{
+    if (ctx)
+        ctx->err = msg;
+    return st;
+}
+
+maize_status_t fail_cuda(maize_ctx_t *ctx, const char *what, cudaError_t e)
+{
+    return fail(ctx, MAIZE_ERR_CUDA, std::string(what) + ": " + cudaGetErrorName(e) + " (" + cudaGetErrorString(e) + ")");
+}
+
+// 2-D bf16 tensor map over a row-major [rows x cols] matrix with row pitch `ld`
+// elements; box = [box_rows x 64 elements], 128-byte swizzle, zero fill outside.
+maize_status_t make_operand_map(maize_ctx_t *ctx, CUtensorMap *map, const void *base, uint64_t rows, uint64_t cols,
+                                uint64_t ld, uint32_t box_rows)
+{
+    cuuint64_t gdim[2] = {cols, rows};
+    cuuint64_t gstride[1] = {ld * 2};
+    cuuint32_t box[2] = {maize::kBlockK, box_rows};
+    cuuint32_t estride[2] = {1, 1};
+    CUresult r = ctx->encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(base), gdim, gstride, box,
+                             estride, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        char buf[160];
+        snprintf(buf, sizeof buf, "cuTensorMapEncodeTiled failed (CUresult %d) for %llu x %llu, ld %llu", (int)r,
+                 (unsigned long long)rows, (unsigned long long)cols, (unsigned long long)ld);
+        return fail(ctx, MAIZE_ERR_CUDA, buf);
+    }
+    return MAIZE_OK;
+}
+
+template <uint32_t BN, uint32_t STAGES>
+maize_status_t launch_variant(maize_ctx_t *ctx, int variant_index, const CUtensorMap &ta, const CUtensorMap &tb,
+                              const GemmParams &p, uint32_t grid, cudaStream_t stream)
+{
+    using L = maize::GemmSmemLayout<BN, STAGES>;
+    auto kernel = maize::gemm_bf16_sm100_1cta<BN, STAGES>;
+    if (!ctx->attr_set[variant_index]) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes);
+        if (e != cudaSuccess)
+            return fail_cuda(ctx, "cudaFuncSetAttribute(max dynamic smem)", e);
+        ctx->attr_set[variant_index] = true;
+    }
+    kernel<<<grid, maize::kNumThreads, L::kDynamicBytes, stream>>>(ta, tb, p);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess)
+        return fail_cuda(ctx, "kernel launch", e);
+    ctx->launches += 1;
+    return MAIZE_OK;
+}
+
+int pick_variant(const maize_ctx_t *ctx, uint32_t m, uint32_t n, uint32_t k)
+{
+    (void)k;
+    if (ctx && ctx->force_kernel >= 1 && ctx->force_kernel <= kNumVariants)
+        return ctx->force_kernel - 1;
+    const uint32_t sms = ctx ? static_cast<uint32_t>(ctx->sm_count) : 148u;
+    const uint64_t tiles_m = (m + maize::kBlockM - 1) / maize::kBlockM;
+    // Widest tile whose tile count still fills the machine reasonably; narrow N gets narrow tiles.
+    if (n <= 32)
+        return 3;
+    if (n <= 64)
+        return 2;
+    const uint64_t tiles256 = tiles_m * ((n + 255) / 256);
+    if (n > 128 && tiles256 >= 2ull * sms)
+        return 0;
+    const uint64_t tiles128 = tiles_m * ((n + 127) / 128);
+    if (n > 128 && tiles256 >= sms) {
+        // between one and two waves of 128x256 tiles: compare wave efficiency with 128x128
+        const double eff256 = double(tiles256) / double(((tiles256 + sms - 1) / sms) * sms);
+        const double eff128 = double(tiles128) / double(((tiles128 + sms - 1) / sms) * sms);
+        return eff256 + 0.05 >= eff128 ? 0 : 1;
+    }
+    if (tiles128 >= sms || n > 64)
+        return 1;
+    return 2;
+}
+
+maize_status_t gemm_impl(maize_ctx_t *ctx, const void *a, uint64_t lda, const void *b, uint64_t ldb, void *c,
+                         uint64_t ldc, uint32_t m, uint32_t n, uint32_t k, cudaStream_t stream)
+{
+    if (!ctx)
+        return MAIZE_ERR_INVALID_ARG;
+    ctx->err.clear();
+    if (m == 0 || n == 0)
+        return MAIZE_OK;
+    if (!c)
+        return fail(ctx, MAIZE_ERR_INVALID_ARG, "C pointer is null");
+    if (ldc < n)
+        return fail(ctx, MAIZE_ERR_INVALID_ARG, "ldc is smaller than N");
+    if (reinterpret_cast<uintptr_t>(c) % 2 != 0)
+        return fail(ctx, MAIZE_ERR_INVALID_ARG, "C must be 2-byte aligned");
+    DeviceGuard guard(ctx->device);
+    if (k == 0) {
+        // empty sum: C = 0
+        cudaError_t e = cudaMemset2DAsync(c, ldc * 2, 0, size_t(n) * 2, m, stream);
+        return e == cudaSuccess ? MAIZE_OK : fail_cuda(ctx, "cudaMemset2DAsync", e);
+    }
+    if (!a || !b)
+        return fail(ctx, MAIZE_ERR_INVALID_ARG, "A or B pointer is null");
+    if (lda < k || ldb < k)
+        return fail(ctx, MAIZE_ERR_INVALID_ARG, "lda/ldb is smaller than K");
+    if (k % 8 != 0 || lda % 8 != 0 || ldb % 8 != 0)
+        return fail(ctx, MAIZE_ERR_UNSUPPORTED, "K, lda and ldb must be multiples of 8 (16-byte TMA row pitch)");
+    if (reinterpret_cast<uintptr_t>(a) % 16 != 0 || reinterpret_cast<uintptr_t>(b) % 16 != 0)
+        return fail(ctx, MAIZE_ERR_UNSUPPORTED, "A and B must be 16-byte aligned");
+    if (lda * 2 >= (1ull << 40) || ldb * 2 >= (1ull << 40))
+        return fail(ctx, MAIZE_ERR_UNSUPPORTED, "row pitch beyond the TMA limit of 2^40 bytes");
+
+    const int vi = pick_variant(ctx, m, n, k);
+    const KernelVariant &kv = kVariants[vi];
+
+    CUtensorMap ta, tb;
+    maize_status_t st = make_operand_map(ctx, &ta, a, m, k, lda, maize::kBlockM);
+    if (st != MAIZE_OK)
+        return st;
+    st = make_operand_map(ctx, &tb, b, n, k, ldb, kv.block_n);
+    if (st != MAIZE_OK)
+        return st;
+
+    GemmParams p;
+    p.c = static_cast<__nv_bfloat16 *>(c);
+    p.ldc = ldc;
+    p.m = m;
+    p.n = n;
+    p.k = k;
+    p.tiles_m = (m + maize::kBlockM - 1) / maize::kBlockM;
+    p.tiles_n = (n + kv.block_n - 1) / kv.block_n;
+    p.group_m = 16;
+    p.c_vec_ok = (ldc % 8 == 0 && reinterpret_cast<uintptr_t>(c) % 16 == 0) ? 1u : 0u;
+    p.status = ctx->d_status;
+    p.timeout_ns = ctx->timeout_ns;
+    const uint64_t tiles = uint64_t(p.tiles_m) * p.tiles_n;
+    if (tiles > 0x7fffffffull)
+        return fail(ctx, MAIZE_ERR_UNSUPPORTED, "too many output tiles");
+    uint32_t cap = static_cast<uint32_t>(ctx->sm_count);
+    if (ctx->max_ctas > 0 && static_cast<uint32_t>(ctx->max_ctas) < cap)
+        cap = static_cast<uint32_t>(ctx->max_ctas);
+    const uint32_t grid = tiles < cap ? static_cast<uint32_t>(tiles) : cap;
+
+    switch (vi) {
+    case 0: return launch_variant<256, 4>(ctx, vi, ta, tb, p, grid, stream);
+    case 1: return launch_variant<128, 6>(ctx, vi, ta, tb, p, grid, stream);
+    case 2: return launch_variant<64, 8>(ctx, vi, ta, tb, p, grid, stream);
+    default: return launch_variant<32, 8>(ctx, vi, ta, tb, p, grid, stream);
+    }
+}
+
+}  // namespace
+
+extern "C" {
+
+int maize_version(void) { return 100; }
+
+const char *maize_status_string(maize_status_t s)
+{
+    switch (s) {
+    case MAIZE_OK: return "ok";
+    case MAIZE_ERR_INVALID_ARG: return "invalid argument";
+    case MAIZE_ERR_UNSUPPORTED: return "unsupported shape or alignment";
+    case MAIZE_ERR_CUDA: return "CUDA error";
+    case MAIZE_ERR_TIMEOUT: return "device wait timed out";
+    case MAIZE_ERR_DEVICE_ABORT: return "device abort";
+    case MAIZE_ERR_NO_DEVICE: return "no CUDA device";
+    }
+    return "unknown status";
+}
+
+maize_status_t maize_ctx_create(int device, maize_ctx_t **out)
+{
+    if (!out)
+        return MAIZE_ERR_INVALID_ARG;
+    *out = nullptr;
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess || count <= 0) {
+        cudaGetLastError();
+        return MAIZE_ERR_NO_DEVICE;
+    }
+    if (device < 0 || device >= count)
+        return MAIZE_ERR_INVALID_ARG;
+    maize_ctx_t *ctx = new (std::nothrow) maize_ctx();
+    if (!ctx)
+        return MAIZE_ERR_CUDA;
+    ctx->device = device;
+    DeviceGuard guard(device);
+    cudaDeviceProp prop;
+    cudaError_t e = cudaGetDeviceProperties(&prop, device);
+    if (e != cudaSuccess) {
+        delete ctx;
+        return MAIZE_ERR_CUDA;
+    }
+    if (prop.major != 10) {
+        // sm_100a code only: refuse loudly instead of failing at the first launch
+        delete ctx;
+        return MAIZE_ERR_UNSUPPORTED;
+    }
+    ctx->sm_count = prop.multiProcessorCount;
+    void *fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+    if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess || !fn) {
+        delete ctx;
+        return MAIZE_ERR_CUDA;
+    }
+    ctx->encode = reinterpret_cast<EncodeTiledFn>(fn);
+    if (cudaMalloc(&ctx->d_status, sizeof(DeviceStatus)) != cudaSuccess ||
+        cudaMemset(ctx->d_status, 0, sizeof(DeviceStatus)) != cudaSuccess ||
+        cudaMallocHost(&ctx->h_status, sizeof(DeviceStatus)) != cudaSuccess) {
+        maize_ctx_destroy(ctx);
+        return MAIZE_ERR_CUDA;
+    }
+    *out = ctx;
+    return MAIZE_OK;
+}
+
+void maize_ctx_destroy(maize_ctx_t *ctx)
+{
+    if (!ctx)
+        return;
+    DeviceGuard guard(ctx->device);
+    if (ctx->d_status)
+        cudaFree(ctx->d_status);
+    if (ctx->h_status)
+        cudaFreeHost(ctx->h_status);
+    if (ctx->staging)
+        cudaFree(ctx->staging);
+    delete ctx;
+}
+
+const char *maize_last_error(const maize_ctx_t *ctx) { return ctx ? ctx->err.c_str() : "null context"; }
+
+maize_status_t maize_gemm_bf16(maize_ctx_t *ctx, const void *a, uint32_t a_rows, uint32_t a_cols, const void *b,
+                               uint32_t b_rows, uint32_t b_cols, void *c, uint32_t c_rows, uint32_t c_cols,
+                               void *cuda_stream)
+{
+    if (!ctx)
+        return MAIZE_ERR_INVALID_ARG;
+    if (a_cols != b_cols)
+        return fail(ctx, MAIZE_ERR_INVALID_ARG, "a_cols != b_cols (both are K; B is stored N x K)");
+    if (c_rows != a_rows || c_cols != b_rows)
+        return fail(ctx, MAIZE_ERR_INVALID_ARG, "C must be a_rows x b_rows");
+    return gemm_impl(ctx, a, a_cols, b, b_cols, c, c_cols, a_rows, b_rows, a_cols, static_cast<cudaStream_t>(cuda_stream));
+}
+
+maize_status_t maize_gemm_bf16_m(maize_ctx_t *ctx, const maize_global_matrix_t *a, const maize_global_matrix_t *b,
+                                 const maize_global_matrix_t *c, void *cuda_stream)
+{
+    if (!ctx)
+        return MAIZE_ERR_INVALID_ARG;
+    if (!a || !b || !c)
+        return fail(ctx, MAIZE_ERR_INVALID_ARG, "null matrix descriptor");
+    return maize_gemm_bf16(ctx, a->ptr, a->nrows, a->ncols, b->ptr, b->nrows, b->ncols, c->ptr, c->nrows, c->ncols,
+                           cuda_stream);
+}
+
+maize_status_t maize_gemm_bf16_ld(maize_ctx_t *ctx, const void *a, uint64_t lda, const void *b, uint64_t ldb, void *c,
+                                  uint64_t ldc, uint32_t m, uint32_t n, uint32_t k, void *cuda_stream)
+{
+    return gemm_impl(ctx, a, lda, b, ldb, c, ldc, m, n, k, static_cast<cudaStream_t>(cuda_stream));
+}
+
+maize_status_t maize_gemm_bf16_host(maize_ctx_t *ctx, const void *a_host, uint32_t a_rows, uint32_t a_cols,
+                                    const void *b_host, uint32_t b_rows, uint32_t b_cols, void *c_host,
+                                    uint32_t c_rows, uint32_t c_cols, void *cuda_stream)
+{
+    if (!ctx)
+        return MAIZE_ERR_INVALID_ARG;
+    if (a_cols != b_cols)
+        return fail(ctx, MAIZE_ERR_INVALID_ARG, "a_cols != b_cols (both are K; B is stored N x K)");
+    if (c_rows != a_rows || c_cols != b_rows)
+        return fail(ctx, MAIZE_ERR_INVALID_ARG, "C must be a_rows x b_rows");
+    if (a_rows == 0 || b_rows == 0)
+        return MAIZE_OK;
+    if (!c_host || ((!a_host || !b_host) && a_cols > 0))
+        return fail(ctx, MAIZE_ERR_INVALID_ARG, "null host pointer");
+    DeviceGuard guard(ctx->device);
+    cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+    auto round_up = [](size_t x) { return (x + 255) & ~size_t(255); };
+    const size_t a_bytes = size_t(a_rows) * a_cols * 2, b_bytes = size_t(b_rows) * b_cols * 2;
+    const size_t c_bytes = size_t(c_rows) * c_cols * 2;
+    const size_t need = round_up(a_bytes) + round_up(b_bytes) + round_up(c_bytes);
+    if (need > ctx->staging_bytes) {
+        if (ctx->staging) {
+            cudaStreamSynchronize(stream);
+            cudaFree(ctx->staging);
+            ctx->staging = nullptr;
+            ctx->staging_bytes = 0;
+        }
+        cudaError_t e = cudaMalloc(&ctx->staging, need);
+        if (e != cudaSuccess)
+            return fail_cuda(ctx, "cudaMalloc(staging)", e);
+        ctx->staging_bytes = need;
+    }
+    char *da = static_cast<char *>(ctx->staging);
+    char *db = da + round_up(a_bytes);
+    char *dc = db + round_up(b_bytes);
+    cudaError_t e;
+    if (a_bytes && (e = cudaMemcpyAsync(da, a_host, a_bytes, cudaMemcpyHostToDevice, stream)) != cudaSuccess)
+        return fail_cuda(ctx, "H2D copy of A", e);
+    if (b_bytes && (e = cudaMemcpyAsync(db, b_host, b_bytes, cudaMemcpyHostToDevice, stream)) != cudaSuccess)
+        return fail_cuda(ctx, "H2D copy of B", e);
+    maize_status_t st = gemm_impl(ctx, da, a_cols, db, b_cols, dc, c_cols, a_rows, b_rows, a_cols, stream);
+    if (st != MAIZE_OK)
+        return st;
+    if ((e = cudaMemcpyAsync(c_host, dc, c_bytes, cudaMemcpyDeviceToHost, stream)) != cudaSuccess)
+        return fail_cuda(ctx, "D2H copy of C", e);
+    if ((e = cudaStreamSynchronize(stream)) != cudaSuccess)
+        return fail_cuda(ctx, "cudaStreamSynchronize", e);
+    return MAIZE_OK;
+}
+
+maize_status_t maize_ctx_poll(maize_ctx_t *ctx, void *cuda_stream)
+{
+    if (!ctx)
+        return MAIZE_ERR_INVALID_ARG;
+    DeviceGuard guard(ctx->device);
+    cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+    cudaError_t e = cudaMemcpyAsync(ctx->h_status, ctx->d_status, sizeof(DeviceStatus), cudaMemcpyDeviceToHost, stream);
+    if (e == cudaSuccess)
+        e = cudaMemsetAsync(ctx->d_status, 0, sizeof(DeviceStatus), stream);
+    if (e == cudaSuccess)
+        e = cudaStreamSynchronize(stream);
+    if (e != cudaSuccess)
+        return fail_cuda(ctx, "status read-back", e);
+    const DeviceStatus s = *ctx->h_status;
+    if (s.code == maize::kStatusOk)
+        return MAIZE_OK;
+    char buf[128];
+    snprintf(buf, sizeof buf, "device status %d raised by role %d of CTA %d", s.code, s.role, s.cta);
+    ctx->err = buf;
+    return s.code == maize::kStatusTimeout ? MAIZE_ERR_TIMEOUT : MAIZE_ERR_DEVICE_ABORT;
+}
+
+maize_status_t maize_ctx_set(maize_ctx_t *ctx, const char *key, int64_t value)
+{
+    if (!ctx || !key)
+        return MAIZE_ERR_INVALID_ARG;
+    if (!strcmp(key, "timeout_ns")) {
+        if (value <= 0)
+            return fail(ctx, MAIZE_ERR_INVALID_ARG, "timeout_ns must be positive");
+        ctx->timeout_ns = static_cast<uint64_t>(value);
+    } else if (!strcmp(key, "force_kernel")) {
+        if (value < 0 || value > kNumVariants)
+            return fail(ctx, MAIZE_ERR_INVALID_ARG, "force_kernel out of range");
+        ctx->force_kernel = static_cast<int>(value);
+    } else if (!strcmp(key, "max_ctas")) {
+        if (value < 0)
+            return fail(ctx, MAIZE_ERR_INVALID_ARG, "max_ctas must be >= 0");
+        ctx->max_ctas = static_cast<int>(value);
+    } else {
+        return fail(ctx, MAIZE_ERR_INVALID_ARG, std::string("unknown key: ") + key);
+    }
+    return MAIZE_OK;
+}
+
+maize_status_t maize_ctx_get(const maize_ctx_t *ctx, const char *key, int64_t *value)
+{
+    if (!ctx || !key || !value)
+        return MAIZE_ERR_INVALID_ARG;
+    if (!strcmp(key, "timeout_ns"))
+        *value = static_cast<int64_t>(ctx->timeout_ns);
+    else if (!strcmp(key, "force_kernel"))
+        *value = ctx->force_kernel;
+    else if (!strcmp(key, "max_ctas"))
+        *value = ctx->max_ctas;
+    else if (!strcmp(key, "sm_count"))
+        *value = ctx->sm_count;
+    else if (!strcmp(key, "device"))
+        *value = ctx->device;
+    else
+        return MAIZE_ERR_INVALID_ARG;
+    return MAIZE_OK;
+}
+
+const char *maize_kernel_name(int id)
+{
+    if (id < 1 || id > kNumVariants)
+        return nullptr;
+    return kVariants[id - 1].name;
+}
+
+int maize_pick_kernel(const maize_ctx_t *ctx, uint32_t m, uint32_t n, uint32_t k) { return pick_variant(ctx, m, n, k) + 1; }
+
+uint64_t maize_ctx_launch_count(const maize_ctx_t *ctx) { return ctx ? ctx->launches : 0; }
+
+maize_status_t maize_debug_wait_expires(maize_ctx_t *ctx, uint64_t budget_ns, void *cuda_stream)
+{
+    if (!ctx)
+        return MAIZE_ERR_INVALID_ARG;
+    if (budget_ns == 0 || budget_ns > 1000000000ull)
+        return fail(ctx, MAIZE_ERR_INVALID_ARG, "budget_ns must be in (0, 1e9]");
+    DeviceGuard guard(ctx->device);
+    maize::wait_expires_kernel<<<1, 32, 0, static_cast<cudaStream_t>(cuda_stream)>>>(ctx->d_status, budget_ns);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess)
+        return fail_cuda(ctx, "kernel launch", e);
+    ctx->launches += 1;
+    return MAIZE_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,169 @@
+"""Host-side mirror of the reference's GEMM call shape over the C ABI.
+
+The reference builds its GEMM from ``Matrix::new(ptr, nrows, ncols)`` pairs
+(crates/maize_tile/src/gmem/matrix.rs:13-18, src/main.rs:46-48) handed to
+``sm80_gemm_smem_multibuffer`` (crates/maize_tile/src/gemm/mod.rs:37-90).  The
+same shape is kept: ``Matrix`` is {ptr, nrows, ncols}; ``Context.gemm`` takes A
+(M x K), B (N x K, K-major) and C (M x N) and launches the sm_100a kernels.
+torch is used only for device memory and streams.
+"""
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+from typing import Optional
+
+from . import _ffi
+
+
+class MaizeError(RuntimeError):
+    def __init__(self, status: int, message: str = ""):
+        self.status = status
+        name = _ffi.STATUS_NAMES.get(status, f"status {status}")
+        super().__init__(f"{name}: {message}" if message else name)
+
+
+@dataclass(frozen=True)
+class Matrix:
+    """{ptr, nrows, ncols} of a dense row-major bf16 matrix in device memory."""
+    ptr: int
+    nrows: int
+    ncols: int
+
+    @classmethod
+    def new(cls, ptr: int, nrows: int, ncols: int) -> "Matrix":
+        return cls(int(ptr), int(nrows), int(ncols))
+
+    @classmethod
+    def from_tensor(cls, t) -> "Matrix":
+        import torch
+        if t.dim() != 2 or t.dtype != torch.bfloat16 or not t.is_contiguous():
+            raise MaizeError(_ffi.INVALID_ARG, "expected a contiguous 2-D bfloat16 tensor")
+        return cls(t.data_ptr(), t.shape[0], t.shape[1])
+
+    def as_c(self) -> _ffi.GlobalMatrix:
+        return _ffi.GlobalMatrix(self.ptr, self.nrows, self.ncols)
+
+
+def _stream_handle(stream) -> Optional[int]:
+    if stream is None:
+        import torch
+        return torch.cuda.current_stream().cuda_stream
+    if isinstance(stream, int):
+        return stream
+    return stream.cuda_stream
+
+
+class Context:
+    """One per host thread / stream; owns the device status word and tunables."""
+
+    def __init__(self, device: int = 0):
+        self._lib = _ffi.load()
+        handle = ctypes.c_void_p()
+        st = self._lib.maize_ctx_create(int(device), ctypes.byref(handle))
+        if st != _ffi.OK:
+            raise MaizeError(st, self._lib.maize_status_string(st).decode())
+        self._h = handle
+        self.device = int(device)
+
+    def close(self) -> None:
+        if getattr(self, "_h", None):
+            self._lib.maize_ctx_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
+
+    # ------------------------------------------------------------ helpers --
+    def _check(self, st: int) -> None:
+        if st != _ffi.OK:
+            raise MaizeError(st, self._lib.maize_last_error(self._h).decode())
+
+    def set(self, key: str, value: int) -> None:
+        self._check(self._lib.maize_ctx_set(self._h, key.encode(), int(value)))
+
+    def get(self, key: str) -> int:
+        out = ctypes.c_int64()
+        self._check(self._lib.maize_ctx_get(self._h, key.encode(), ctypes.byref(out)))
+        return out.value
+
+    @property
+    def launch_count(self) -> int:
+        return int(self._lib.maize_ctx_launch_count(self._h))
+
+    def pick_kernel(self, m: int, n: int, k: int) -> str:
+        return self._lib.maize_kernel_name(self._lib.maize_pick_kernel(self._h, m, n, k)).decode()
+
+    def poll(self, stream=None) -> None:
+        """Synchronise the stream and raise if a device wait timed out."""
+        self._check(self._lib.maize_ctx_poll(self._h, _stream_handle(stream)))
+
+    # --------------------------------------------------------------- GEMM --
+    def gemm_matrices(self, a: Matrix, b: Matrix, c: Matrix, stream=None) -> None:
+        """C = A @ B.T through the {ptr, nrows, ncols} bundles."""
+        ca, cb, cc = a.as_c(), b.as_c(), c.as_c()
+        self._check(self._lib.maize_gemm_bf16_m(self._h, ctypes.byref(ca), ctypes.byref(cb), ctypes.byref(cc),
+                                                _stream_handle(stream)))
+
+    def gemm_raw(self, a_ptr, a_rows, a_cols, b_ptr, b_rows, b_cols, c_ptr, c_rows, c_cols, stream=None) -> None:
+        self._check(self._lib.maize_gemm_bf16(self._h, a_ptr, a_rows, a_cols, b_ptr, b_rows, b_cols, c_ptr, c_rows,
+                                              c_cols, _stream_handle(stream)))
+
+    def gemm_ld(self, a_ptr, lda, b_ptr, ldb, c_ptr, ldc, m, n, k, stream=None) -> None:
+        self._check(self._lib.maize_gemm_bf16_ld(self._h, a_ptr, lda, b_ptr, ldb, c_ptr, ldc, m, n, k,
+                                                 _stream_handle(stream)))
+
+    def gemm_host(self, a_ptr, a_rows, a_cols, b_ptr, b_rows, b_cols, c_ptr, c_rows, c_cols, stream=None) -> None:
+        """Host buffers in, host buffer out; copies and the wait are inside the call."""
+        self._check(self._lib.maize_gemm_bf16_host(self._h, a_ptr, a_rows, a_cols, b_ptr, b_rows, b_cols, c_ptr,
+                                                   c_rows, c_cols, _stream_handle(stream)))
+
+    def gemm(self, a, b, out=None, stream=None):
+        """``out = a @ b.T`` for bf16 CUDA tensors: a is M x K, b is N x K; rows may be strided."""
+        import torch
+        for name, t in (("a", a), ("b", b)):
+            if t.dim() != 2 or t.dtype != torch.bfloat16 or not t.is_cuda or (t.shape[1] > 1 and t.stride(1) != 1):
+                raise MaizeError(_ffi.INVALID_ARG, f"{name}: expected a 2-D bfloat16 CUDA tensor with unit column stride")
+        m, k = a.shape
+        n, kb = b.shape
+        if k != kb:
+            raise MaizeError(_ffi.INVALID_ARG, "a.shape[1] != b.shape[1] (b is stored N x K)")
+        if out is None:
+            out = torch.empty((m, n), dtype=torch.bfloat16, device=a.device)
+        elif out.shape != (m, n) or out.dtype != torch.bfloat16 or not out.is_cuda or (n > 1 and out.stride(1) != 1):
+            raise MaizeError(_ffi.INVALID_ARG, "out: expected an M x N bfloat16 CUDA tensor with unit column stride")
+        lda = a.stride(0) if m > 1 else max(k, 1)
+        ldb = b.stride(0) if n > 1 else max(k, 1)
+        ldc = out.stride(0) if m > 1 else max(n, 1)
+        self.gemm_ld(a.data_ptr(), lda, b.data_ptr(), ldb, out.data_ptr(), ldc, m, n, k, stream)
+        return out
+
+    def debug_wait_expires(self, budget_ns: int, stream=None) -> None:
+        self._check(self._lib.maize_debug_wait_expires(self._h, int(budget_ns), _stream_handle(stream)))
+
+
+_default_ctx = {}
+
+
+def default_context(device: Optional[int] = None) -> Context:
+    import torch
+    if device is None:
+        device = torch.cuda.current_device()
+    ctx = _default_ctx.get(device)
+    if ctx is None:
+        ctx = _default_ctx[device] = Context(device)
+    return ctx
+
+
+def gemm(a, b, out=None, stream=None):
+    """``a @ b.T`` on the B200 kernels (module-level convenience over a cached Context)."""
+    return default_context(a.device.index).gemm(a, b, out=out, stream=stream)

@@ -1,0 +1,95 @@
+"""CPU checks of the C-ABI boundary: the library builds, loads without a GPU, and exports
+exactly what include/maize_gemm.h declares.  No compute call is made here."""
+import ctypes
+import re
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parent.parent
+HEADER = ROOT / "include" / "maize_gemm.h"
+
+
+def declared_symbols():
+    text = re.sub(r"/\*.*?\*/", "", HEADER.read_text(), flags=re.S)
+    return sorted(set(re.findall(r"MAIZE_API[^;(]*?\b(maize_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_lists_entry_points():
+    names = declared_symbols()
+    for must in ("maize_gemm_bf16", "maize_gemm_bf16_m", "maize_gemm_bf16_ld", "maize_gemm_bf16_host",
+                 "maize_ctx_create", "maize_ctx_destroy", "maize_ctx_poll"):
+        assert must in names
+
+
+def test_library_exports_every_declared_symbol():
+    from maize_b200 import _ffi, build
+    build.build()
+    lib = ctypes.CDLL(str(_ffi.LIB_PATH))
+    for name in declared_symbols():
+        assert hasattr(lib, name), f"{name} is declared in maize_gemm.h but not exported"
+
+
+def test_binding_covers_the_header():
+    from maize_b200 import _ffi
+    assert sorted(_ffi.SYMBOLS) == declared_symbols()
+    _ffi.load()
+
+
+def test_header_compiles_as_plain_c(tmp_path):
+    import subprocess
+    src = tmp_path / "t.c"
+    src.write_text('#include "maize_gemm.h"\n'
+                   "_Static_assert(sizeof(maize_global_matrix_t) == 16, \"16-byte bundle\");\n"
+                   "_Static_assert(_Alignof(maize_global_matrix_t) == 16, \"16-byte aligned\");\n"
+                   "int main(void) { return MAIZE_OK; }\n")
+    subprocess.run(["gcc", "-std=c11", "-Wall", "-Werror", "-I", str(ROOT / "include"), "-c", str(src), "-o",
+                    str(tmp_path / "t.o")], check=True)
+
+
+def test_status_strings_and_kernel_table():
+    from maize_b200 import _ffi
+    lib = _ffi.load()
+    assert lib.maize_version() >= 100
+    for code in range(7):
+        assert lib.maize_status_string(code)
+    names = []
+    i = 1
+    while lib.maize_kernel_name(i):
+        names.append(lib.maize_kernel_name(i).decode())
+        i += 1
+    assert names and all(n.startswith("sm100_") for n in names)
+    assert lib.maize_kernel_name(0) is None
+
+
+def test_no_device_is_reported_not_hidden():
+    """Without a GPU the context constructor fails with NO_DEVICE: there is no CPU path to fall back to."""
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    import maize_b200
+    with pytest.raises(maize_b200.MaizeError) as e:
+        maize_b200.Context(0)
+    assert e.value.status == maize_b200._ffi.NO_DEVICE
+
+
+def test_null_context_is_rejected():
+    from maize_b200 import _ffi
+    lib = _ffi.load()
+    assert lib.maize_gemm_bf16(None, None, 1, 8, None, 1, 8, None, 1, 1, None) == _ffi.INVALID_ARG
+    assert lib.maize_ctx_poll(None, None) == _ffi.INVALID_ARG
+    assert lib.maize_ctx_create(0, None) == _ffi.INVALID_ARG
+
+
+def test_tile_descriptors_keep_reference_names():
+    from maize_b200.tile import DType, Shape, Stride, Tile
+    assert DType.from_str("F32") is DType.F32 and DType.try_from_str("nope") is None
+    with pytest.raises(ValueError):
+        DType.from_str("F16")
+    s = Shape(128, Shape(8, 8))
+    assert s.size() == 8192 and repr(s) == "(128, (8, 8))" and s == Shape(128, Shape(8, 8))
+    assert Stride(64, 1) != Shape(64, 1)
+    t = Tile(Shape(128, 64), DType.BF16)
+    assert repr(t) == "Tile(shape=(128, 64), dtype=BF16)" and t.nbytes() == 16384
+    with pytest.raises(TypeError):
+        Tile((128, 64), DType.BF16)

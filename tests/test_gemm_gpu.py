@@ -1,0 +1,213 @@
+"""GPU parity tests: the CUDA path, called through the C ABI, against the CPU oracle on the same
+seeded inputs.  Ordered from the safest launch to the largest."""
+import numpy as np
+import pytest
+
+from helpers import CONFIGS, assert_parity, make_inputs, to_device, to_host
+
+pytestmark = pytest.mark.gpu
+
+
+def run_case(ctx, oracle, m, n, k, seed=0, force=0, **dist):
+    import torch
+    a, b = make_inputs(oracle, m, n, k, seed, **dist)
+    da, db = to_device(a), to_device(b)
+    dc = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+    ctx.set("force_kernel", force)
+    try:
+        ctx.gemm_raw(da.data_ptr(), m, k, db.data_ptr(), n, k, dc.data_ptr(), m, n)
+        ctx.poll()
+    finally:
+        ctx.set("force_kernel", 0)
+    ref = oracle.gemm_bf16(a, b)
+    return assert_parity(oracle, to_host(dc), ref, k, oracle.max_abs_bf16(a), oracle.max_abs_bf16(b),
+                         what=f"{m}x{n}x{k} kernel {force}")
+
+
+def test_bounded_wait_returns_timeout(ctx):
+    """A wait that nothing satisfies ends by itself and is reported, and the context stays usable."""
+    import maize_b200
+    ctx.debug_wait_expires(200_000)  # 0.2 ms budget
+    with pytest.raises(maize_b200.MaizeError) as e:
+        ctx.poll()
+    assert e.value.status == maize_b200._ffi.TIMEOUT
+    ctx.poll()  # the status word was cleared
+
+
+@pytest.mark.parametrize("force", [1, 2, 3, 4])
+def test_single_tile_single_kblock(ctx, oracle, force):
+    run_case(ctx, oracle, 128, 256, 64, seed=10, force=force)
+
+
+@pytest.mark.parametrize("force", [1, 2, 3, 4])
+def test_ring_wraps(ctx, oracle, force):
+    # more k-blocks than stages: every barrier changes phase several times
+    run_case(ctx, oracle, 128, 256, 64 * 21, seed=11, force=force)
+
+
+@pytest.mark.parametrize("force", [1, 2, 3, 4])
+def test_many_tiles_per_cta(ctx, oracle, force):
+    # more tiles than SMs for every variant: both TMEM accumulator buffers and their phases cycle
+    run_case(ctx, oracle, 128 * 10, 256 * 9, 256, seed=12, force=force)
+
+
+@pytest.mark.parametrize("m,n,k", [
+    (1, 1, 8), (1, 8, 8), (7, 5, 16), (130, 250, 72), (127, 33, 520), (300, 1000, 136), (129, 257, 64),
+    (128, 255, 128), (513, 77, 1032), (64, 4096, 256), (2000, 24, 512),
+])
+@pytest.mark.parametrize("force", [0, 1, 2, 3, 4])
+def test_ragged_edges(ctx, oracle, m, n, k, force):
+    run_case(ctx, oracle, m, n, k, seed=13, force=force)
+
+
+def test_canaries_around_c(ctx, oracle):
+    """Nothing is written outside C: rows of padding between C rows (ldc > N) and guard bands stay intact."""
+    import torch
+    m, n, k, ldc = 200, 333, 136, 340
+    a, b = make_inputs(oracle, m, n, k, 14)
+    da, db = to_device(a), to_device(b)
+    guard = 1024
+    buf = torch.full((guard + m * ldc + guard,), 7.0, dtype=torch.bfloat16, device="cuda")
+    c_ptr = buf.data_ptr() + guard * 2
+    ctx.gemm_ld(da.data_ptr(), k, db.data_ptr(), k, c_ptr, ldc, m, n, k)
+    ctx.poll()
+    host = to_host(buf)
+    seven = to_host(torch.full((1,), 7.0, dtype=torch.bfloat16))[0]
+    assert np.all(host[:guard] == seven) and np.all(host[guard + m * ldc:] == seven)
+    body = host[guard:guard + m * ldc].reshape(m, ldc)
+    assert np.all(body[:, n:] == seven)
+    assert_parity(oracle, np.ascontiguousarray(body[:, :n]), oracle.gemm_bf16(a, b), k, oracle.max_abs_bf16(a),
+                  oracle.max_abs_bf16(b), "strided C")
+
+
+def test_strided_operands(ctx, oracle):
+    """Row slabs / column slices as used by the N-sharded path: lda, ldb > K and ldc > N."""
+    import torch
+    m, n, k = 260, 300, 192
+    a, b = make_inputs(oracle, m, n, 2 * k, 15)
+    da, db = to_device(a), to_device(b)
+    full_c = torch.zeros((m, 2 * n), dtype=torch.bfloat16, device="cuda")
+    out = ctx.gemm(da[:, k:], db[:, :k], out=full_c[:, n:])
+    ctx.poll()
+    assert out.data_ptr() == full_c[:, n:].data_ptr()
+    ref = oracle.gemm_bf16(np.ascontiguousarray(a[:, k:]), np.ascontiguousarray(b[:, :k]))
+    assert_parity(oracle, to_host(full_c[:, n:]), ref, k, oracle.max_abs_bf16(a), oracle.max_abs_bf16(b), "strided")
+    assert not to_host(full_c[:, :n]).any()
+
+
+def test_k_zero_and_empty(ctx, oracle):
+    import torch
+    c = torch.full((5, 9), 3.0, dtype=torch.bfloat16, device="cuda")
+    a = torch.zeros((5, 0), dtype=torch.bfloat16, device="cuda")
+    b = torch.zeros((9, 0), dtype=torch.bfloat16, device="cuda")
+    ctx.gemm(a, b, out=c)
+    ctx.poll()
+    assert not to_host(c).any()
+    ctx.gemm_raw(0, 0, 64, 0, 9, 64, 0, 0, 9)  # M == 0: nothing to do, no pointer is touched
+
+
+def test_argument_errors(ctx):
+    import torch
+    import maize_b200
+    E = maize_b200._ffi
+    a = torch.zeros((16, 64), dtype=torch.bfloat16, device="cuda")
+    b = torch.zeros((8, 64), dtype=torch.bfloat16, device="cuda")
+    c = torch.zeros((16, 8), dtype=torch.bfloat16, device="cuda")
+    cases = [
+        (lambda: ctx.gemm_raw(a.data_ptr(), 16, 64, b.data_ptr(), 8, 32, c.data_ptr(), 16, 8), E.INVALID_ARG),
+        (lambda: ctx.gemm_raw(a.data_ptr(), 16, 64, b.data_ptr(), 8, 64, c.data_ptr(), 16, 9), E.INVALID_ARG),
+        (lambda: ctx.gemm_raw(a.data_ptr(), 16, 64, b.data_ptr(), 8, 64, 0, 16, 8), E.INVALID_ARG),
+        (lambda: ctx.gemm_raw(0, 16, 64, b.data_ptr(), 8, 64, c.data_ptr(), 16, 8), E.INVALID_ARG),
+        (lambda: ctx.gemm_raw(a.data_ptr(), 16, 60, b.data_ptr(), 8, 60, c.data_ptr(), 16, 8), E.UNSUPPORTED),
+        (lambda: ctx.gemm_raw(a.data_ptr() + 2, 15, 64, b.data_ptr(), 8, 64, c.data_ptr(), 15, 8), E.UNSUPPORTED),
+        (lambda: ctx.gemm_ld(a.data_ptr(), 32, b.data_ptr(), 64, c.data_ptr(), 8, 16, 8, 64), E.INVALID_ARG),
+        (lambda: ctx.gemm_ld(a.data_ptr(), 64, b.data_ptr(), 64, c.data_ptr(), 4, 16, 8, 64), E.INVALID_ARG),
+    ]
+    for call, status in cases:
+        with pytest.raises(maize_b200.MaizeError) as e:
+            call()
+        assert e.value.status == status
+    ctx.poll()
+
+
+def test_matrix_bundle_entry_point(ctx, oracle):
+    import torch
+    import maize_b200
+    m, n, k = 96, 72, 128
+    a, b = make_inputs(oracle, m, n, k, 16)
+    da, db = to_device(a), to_device(b)
+    dc = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+    M = maize_b200.Matrix
+    ctx.gemm_matrices(M.from_tensor(da), M.from_tensor(db), M.new(dc.data_ptr(), m, n))
+    ctx.poll()
+    assert_parity(oracle, to_host(dc), oracle.gemm_bf16(a, b), k, oracle.max_abs_bf16(a), oracle.max_abs_bf16(b))
+
+
+def test_host_entry_point(ctx, oracle):
+    """Host buffers in and out through maize_gemm_bf16_host (pinned and pageable)."""
+    import torch
+    m, n, k = 300, 520, 264
+    a, b = make_inputs(oracle, m, n, k, 17)
+    ref = oracle.gemm_bf16(a, b)
+    c = np.zeros((m, n), dtype=np.uint16)
+    ctx.gemm_host(a.ctypes.data, m, k, b.ctypes.data, n, k, c.ctypes.data, m, n)
+    ctx.poll()
+    assert_parity(oracle, c, ref, k, oracle.max_abs_bf16(a), oracle.max_abs_bf16(b), "pageable host")
+    pa = torch.from_numpy(a.view(np.int16)).pin_memory()
+    pb = torch.from_numpy(b.view(np.int16)).pin_memory()
+    pc = torch.zeros((m, n), dtype=torch.int16).pin_memory()
+    ctx.gemm_host(pa.data_ptr(), m, k, pb.data_ptr(), n, k, pc.data_ptr(), m, n)
+    ctx.poll()
+    assert np.array_equal(pc.numpy().view(np.uint16), c)
+
+
+@pytest.mark.parametrize("name", ["c1", "c2", "c3"])
+def test_baseline_configs_full(ctx, oracle, name):
+    m, n, k, da, sa, db, sb, seed = CONFIGS[name]
+    run_case(ctx, oracle, m, n, k, seed=seed, dist_a=da, scale_a=sa, dist_b=db, scale_b=sb)
+
+
+def test_deterministic_across_launches(ctx, oracle):
+    import torch
+    m, n, k = 1024, 2048, 512
+    a, b = make_inputs(oracle, m, n, k, 18)
+    da, db = to_device(a), to_device(b)
+    c1 = ctx.gemm(da, db)
+    c2 = ctx.gemm(da, db)
+    ctx.poll()
+    assert torch.equal(c1.view(torch.int16), c2.view(torch.int16))
+
+
+@pytest.mark.parametrize("name", ["c4", "c5", "t"])
+def test_large_configs_sampled_and_properties(ctx, oracle, name):
+    """Full-size shapes: sampled rows against the oracle, the whole matrix against an fp32 matmul on the
+    GPU (a library call used as a second checker only), and linearity in A as a size-independent property."""
+    import torch
+    m, n, k, da_, sa, db_, sb, seed = CONFIGS[name]
+    a, b = make_inputs(oracle, m, n, k, seed, da_, sa, db_, sb)
+    da, db = to_device(a), to_device(b)
+    dc = ctx.gemm(da, db)
+    ctx.poll()
+    ma, mb = oracle.max_abs_bf16(a), oracle.max_abs_bf16(b)
+    rows = np.unique(np.concatenate([np.arange(0, 8), np.arange(m - 8, m),
+                                     np.random.default_rng(seed).integers(0, m, 48)]))
+    ref_rows = oracle.gemm_bf16(np.ascontiguousarray(a[rows]), b)
+    got_rows = to_host(dc[torch.from_numpy(rows).cuda()])
+    assert_parity(oracle, got_rows, ref_rows, k, ma, mb, f"{name} sampled rows")
+    # whole matrix against fp32 matmul of the widened operands, in row slabs to bound memory
+    old = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        bf = db.float()
+        tol = 1e-4 * float(np.sqrt(k)) * ma * mb
+        for r0 in range(0, m, 2048):
+            ref = da[r0:r0 + 2048].float() @ bf.T
+            err = (dc[r0:r0 + 2048].float() - ref).abs() - ref.abs() * 2.0 ** -7
+            assert float(err.max()) <= tol, f"{name} rows {r0}..: {float(err.max())} > {tol}"
+        del bf
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = old
+    # linearity: (2A) B^T == 2 (A B^T) exactly (power-of-two scaling commutes with every rounding)
+    c2 = ctx.gemm(da * 2, db)
+    ctx.poll()
+    assert torch.equal((dc * 2).view(torch.int16), c2.view(torch.int16))
