@@ -48,6 +48,7 @@ def parse_args():
     p.add_argument("--slabs", type=int, default=8, help="row slabs of A for the overlapped broadcast (N > 1)")
     p.add_argument("--e2e-steps", type=int, default=3)
     p.add_argument("--no-cpu-baseline", action="store_true")
+    p.add_argument("--force-kernel", type=int, default=0, help="kernel variant id (0 = the library's heuristic)")
     p.add_argument("--cpu-seconds", type=float, default=10.0, help="target CPU time of the cpu_baseline sample")
     return p.parse_args()
 
@@ -208,6 +209,8 @@ def main():
     lo, hi = shard_bounds(n, world, rank)
     ns = hi - lo
     ctx = maize_b200.Context(local_rank)
+    if args.force_kernel:
+        ctx.set("force_kernel", args.force_kernel)
     gen = torch.Generator(device=dev)
     gen.manual_seed(seed)  # every rank draws the same A; B rows are taken from a per-rank stream
 
@@ -216,19 +219,26 @@ def main():
             return ((torch.rand(shape, device=dev, generator=g) * 2 - 1) * sigma).to(torch.bfloat16)
         return (torch.randn(shape, device=dev, generator=g) * sigma).to(torch.bfloat16)
 
-    a_root = draw((m, k), sa, gen) if rank == 0 else None
     gen_b = torch.Generator(device=dev)
     gen_b.manual_seed(1000 + seed * 16 + rank)
-    b_shard = draw((ns, k), sb, gen_b)
-    c_shard = torch.empty((m, ns), dtype=torch.bfloat16, device=dev)
-    op = NShardedGemm(m, n, k, slabs=args.slabs, ctx=ctx, device=dev)
-
     total_bytes = 2 * (m * k + n * k + m * n)
-    small = 2 * (m * k + ns * k + m * ns) < 2 * L2_BYTES
-    flush_buf = torch.empty(2 * L2_BYTES // 4, dtype=torch.float32, device=dev) if small else None
+    rank_bytes = 2 * (m * k + ns * k + m * ns)
+    # Inputs that fit in L2 would be served from it on back-to-back launches: rotate over enough
+    # independent input sets that the bytes touched between two uses of a set exceed 4x L2.
+    small = rank_bytes < 2 * L2_BYTES
+    n_sets = max(1, -(-4 * L2_BYTES // rank_bytes)) if small else 1
+    sets = []
+    for _ in range(n_sets):
+        sets.append((draw((m, k), sa, gen) if rank == 0 else None, draw((ns, k), sb, gen_b),
+                     torch.empty((m, ns), dtype=torch.bfloat16, device=dev)))
+    a_root, b_shard, c_shard = sets[0]
+    op = NShardedGemm(m, n, k, slabs=args.slabs, ctx=ctx, device=dev)
+    step_no = [0]
 
     def step():
-        op.run(a_root, b_shard, c_shard)
+        a_i, b_i, c_i = sets[step_no[0] % n_sets]
+        step_no[0] += 1
+        op.run(a_i, b_i, c_i)
 
     def sync_all():
         if world > 1:
@@ -247,27 +257,14 @@ def main():
 
     launches0 = ctx.launch_count
     t_wall0 = time.time()
-    if small:
-        # inputs fit in L2: flush it before every timed iteration and time each iteration alone
-        evs = []
-        for _ in range(args.steps):
-            flush_buf.zero_()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            step()
-            e1.record()
-            evs.append((e0, e1))
-        sync_all()
-        ms_total = sum(a.elapsed_time(b) for a, b in evs)
-    else:
-        sync_all()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(args.steps):
-            step()
-        e1.record()
-        sync_all()
-        ms_total = e0.elapsed_time(e1)
+    sync_all()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    sync_all()
+    ms_total = e0.elapsed_time(e1)
     t_wall1 = time.time()
     launches = ctx.launch_count - launches0
     ctx.poll()
@@ -287,19 +284,18 @@ def main():
 
     # kernel-only time on this rank (for the roofline): one GEMM over the rank's whole shard, A resident
     a_res = a_root if rank == 0 else op.a_buffer(b_shard)
-    reps = max(3, min(args.steps, 10))
-    k_ms = []
-    for _ in range(reps):
-        if small:
-            flush_buf.zero_()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        ctx.gemm(a_res, b_shard, out=c_shard)
-        e1.record()
-        torch.cuda.synchronize()
-        k_ms.append(e0.elapsed_time(e1))
-    kernel_ms = sum(k_ms) / len(k_ms)
-    kernel_name = ctx.pick_kernel(m, ns, k)
+    reps = max(3, min(args.steps, 10)) * n_sets
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(reps):
+        _, b_i, c_i = sets[i % n_sets]
+        a_i = sets[i % n_sets][0] if rank == 0 else a_res
+        ctx.gemm(a_i, b_i, out=c_i)
+    e1.record()
+    torch.cuda.synchronize()
+    kernel_ms = e0.elapsed_time(e1) / reps
+    kernel_name = ctx.pick_kernel(m // len(op.slabs) if world > 1 else m, ns, k)
 
     # ---- end to end through the host-buffer entry point (N = 1) or pinned copies + sharded step (N > 1)
     e2e = None
@@ -382,8 +378,8 @@ def main():
                        "layout": "A MxK row-major, B NxK K-major, C MxN bf16",
                        "parallelism": "single GPU" if world == 1 else
                                       f"N-sharded x{world}, A broadcast from rank 0 over NCCL in {len(op.slabs)} row slabs",
-                       "l2": "L2 flushed (256 MiB write) before each timed iteration" if small else
-                             "inputs exceed L2 (back-to-back launches)",
+                       "l2": (f"rotating over {n_sets} independent input sets ({n_sets * rank_bytes >> 20} MiB > 4x L2), "
+                              "back-to-back launches") if small else "inputs exceed L2 (back-to-back launches)",
                        "algorithmic_bytes": total_bytes},
             "roofline": roof, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
         }

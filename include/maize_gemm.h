@@ -134,7 +134,9 @@ MAIZE_API maize_status_t maize_gemm_bf16_host(maize_ctx_t *ctx, const void *a_ho
 MAIZE_API maize_status_t maize_ctx_poll(maize_ctx_t *ctx, void *cuda_stream);
 
 /* Tunables.  Keys: "timeout_ns" (device wait budget), "force_kernel" (0 = heuristic,
- * see maize_kernel_name), "max_ctas" (cap on the persistent grid, 0 = SM count). */
+ * see maize_kernel_name), "max_ctas" (cap on the persistent grid, 0 = SM count),
+ * "profile" (1 = per-CTA cycle accounting, see maize_ctx_read_profile), "debug_flags"
+ * (performance diagnostics that make results WRONG: 1 = all loads hit one tile, 2 = no loads). */
 MAIZE_API maize_status_t maize_ctx_set(maize_ctx_t *ctx, const char *key, int64_t value);
 MAIZE_API maize_status_t maize_ctx_get(const maize_ctx_t *ctx, const char *key, int64_t *value);
 
@@ -145,6 +147,16 @@ MAIZE_API int maize_pick_kernel(const maize_ctx_t *ctx, uint32_t m, uint32_t n, 
 
 /* Number of kernels this context has launched since creation. */
 MAIZE_API uint64_t maize_ctx_launch_count(const maize_ctx_t *ctx);
+
+/*
+ * Debugging aid with no counterpart in the reference: after maize_ctx_set(ctx, "profile", 1)
+ * every GEMM launch records, per CTA, 8 cycle counters (producer blocked on a free stage, MMA
+ * blocked on data, MMA blocked on a free accumulator, epilogue blocked on a finished
+ * accumulator, epilogue draining, CTA lifetime, tiles done, spare).  Copies the counters of
+ * the last launch (8 * CTAs values) to `out` after synchronising the stream; returns the
+ * number of CTAs written (at most max_ctas).
+ */
+MAIZE_API int maize_ctx_read_profile(maize_ctx_t *ctx, uint64_t *out, int max_ctas, void *cuda_stream);
 
 /*
  * Self-test of the bounded-wait machinery: launches one CTA that waits on a

@@ -45,6 +45,7 @@ SYMBOLS = {
     "maize_pick_kernel": (_int, [_vp, _u32, _u32, _u32]),
     "maize_ctx_launch_count": (_u64, [_vp]),
     "maize_debug_wait_expires": (_int, [_vp, _u64, _vp]),
+    "maize_ctx_read_profile": (_int, [_vp, ctypes.POINTER(_u64), _int, _vp]),
 }
 
 _lib = None

@@ -1,0 +1,213 @@
+// Pieces shared by the sm_100a GEMM kernels: the device status word, bounded
+// mbarrier waits, the tile order, kernel parameters and the bf16 epilogue.
+#pragma once
+#include "ptx_sm100.cuh"
+
+namespace maize {
+
+constexpr int kStatusOk = 0;
+constexpr int kStatusTimeout = 4;      // == MAIZE_ERR_TIMEOUT
+constexpr int kStatusDeviceAbort = 5;  // == MAIZE_ERR_DEVICE_ABORT
+
+// Device status block: worst status code, role that gave up, its CTA, spare.
+struct DeviceStatus {
+    int code;
+    int role;
+    int cta;
+    int detail;
+};
+
+constexpr uint32_t kBlockM = 128;  // rows of C per CTA = TMEM lanes
+constexpr uint32_t kBlockK = 64;   // bf16 elements per k-block = one 128-byte swizzle row
+constexpr uint32_t kUmmaK = 16;    // K per tcgen05.mma for 16-bit operands
+constexpr uint32_t kNumThreads = 192;
+constexpr uint32_t kNumEpilogueThreads = 128;
+constexpr uint32_t kNumEpilogueWarps = 4;
+
+// Per-warp staging for the ragged epilogue: 32 rows of 32 bf16 (64 B) padded to
+// 80 B so that the 16-byte row writes of a quarter warp hit distinct banks.
+constexpr uint32_t kStageRowBytes = 80;
+constexpr uint32_t kStageWarpBytes = 32 * kStageRowBytes;
+constexpr uint32_t kStageBytesTotal = kNumEpilogueWarps * kStageWarpBytes;
+
+struct WaitCtl {
+    volatile int *abort_flag;  // shared memory, CTA-wide
+    DeviceStatus *status;      // global memory
+    uint64_t budget_ns;
+};
+
+__device__ __forceinline__ void record_timeout(const WaitCtl &ctl, int role)
+{
+    *ctl.abort_flag = 1;
+    if (atomicMax(&ctl.status->code, kStatusTimeout) < kStatusTimeout) {
+        ctl.status->role = role;
+        ctl.status->cta = static_cast<int>(blockIdx.x);
+    }
+}
+
+// Bounded wait on an mbarrier phase.  Returns false if the budget ran out or
+// another role of this CTA already gave up.  CLUSTER = acquire at cluster scope
+// (the barrier is completed by arrivals or copies of the peer CTA).
+template <bool CLUSTER = false>
+__device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity, const WaitCtl &ctl, int role)
+{
+    auto probe = [&]() { return CLUSTER ? ptx::mbar_try_wait_cluster(bar, parity) : ptx::mbar_try_wait(bar, parity); };
+    if (probe())
+        return true;
+    const uint64_t t0 = ptx::global_timer_ns();
+    for (uint32_t it = 1;; ++it) {
+        if (probe())
+            return true;
+        if ((it & 31u) == 0u) {
+            if (*ctl.abort_flag)
+                return false;
+            if (ptx::global_timer_ns() - t0 > ctl.budget_ns) {
+                record_timeout(ctl, role);
+                return false;
+            }
+        }
+    }
+}
+
+// Tile order: groups of `group_m` row-blocks sweep all column-blocks, so that the
+// CTAs running at one time share A row panels and B column panels in L2.  This
+// is the grid-stride over (row panel, column panel) pairs of the reference
+// (src/main.rs:56-73, crates/maize_tile/src/gmem/row_panel.rs:95-109) with an
+// L2-aware order.
+struct TileCoord {
+    uint32_t m_blk, n_blk;
+};
+
+__device__ __forceinline__ TileCoord tile_coord(uint32_t t, uint32_t tiles_m, uint32_t tiles_n, uint32_t group_m)
+{
+    const uint32_t per_group = group_m * tiles_n;
+    const uint32_t g = t / per_group;
+    const uint32_t first_m = g * group_m;
+    const uint32_t rows = min(tiles_m - first_m, group_m);
+    const uint32_t r = t - g * per_group;
+    TileCoord c;
+    c.m_blk = first_m + r % rows;
+    c.n_blk = r / rows;
+    return c;
+}
+
+struct GemmParams {
+    __nv_bfloat16 *c;
+    uint64_t ldc;  // elements
+    uint32_t m, n, k;
+    uint32_t tiles_m, tiles_n;  // in units of the kernel's tile (per CTA pair for the 2-CTA kernel)
+    uint32_t group_m;
+    uint32_t c_vec_ok;  // 1: every C row starts 16-byte aligned (ldc % 8 == 0 and base aligned)
+    DeviceStatus *status;
+    uint64_t timeout_ns;
+    // Optional per-CTA cycle accounting (null in normal use): kProfileSlots counters per CTA.
+    unsigned long long *profile;
+    // Diagnostic switches for performance analysis (0 in normal use; results are wrong when set):
+    //   bit 0: every load fetches tile (0, 0), so all operand traffic hits in L2;
+    //   bit 1: no loads at all, the producer only signals "full" (upper bound of the MMA issue path).
+    uint32_t debug_flags;
+};
+
+// Slots of the per-CTA profile: cycles a role spent blocked in its waits, and the CTA's lifetime.
+enum ProfileSlot {
+    kProfProducerWaitEmpty = 0,
+    kProfMmaWaitFull = 1,
+    kProfMmaWaitAccEmpty = 2,
+    kProfEpilogueWaitAccFull = 3,
+    kProfEpilogueDrain = 4,
+    kProfCtaCycles = 5,
+    kProfTiles = 6,
+    kProfileSlots = 8
+};
+
+// Adds the cycles of one wait to a role-local counter when profiling is on.
+struct WaitTimer {
+    bool on;
+    long long t0;
+    __device__ __forceinline__ explicit WaitTimer(bool enabled) : on(enabled), t0(enabled ? ptx::sm_clock64() : 0) {}
+    __device__ __forceinline__ void stop(unsigned long long &acc)
+    {
+        if (on)
+            acc += static_cast<unsigned long long>(ptx::sm_clock64() - t0);
+    }
+};
+
+// Store one 32-row x 32-column chunk of C held by a warp as 32 fp32 accumulators
+// per lane (lane = row).  `row0` is the first of the warp's 32 rows, `col0` the
+// first column; both are warp-uniform, so every branch below is too.
+//   aligned + full chunk : four 16-byte stores per lane straight from registers
+//   otherwise            : transpose through the warp's staging buffer and write
+//                          each row as one run of consecutive 2-byte elements
+//                          (coalesced, any alignment), masked at the M and N edges.
+__device__ __forceinline__ void store_chunk(const GemmParams &p, uint8_t *stage_warp, uint32_t row0, uint32_t col0,
+                                            uint32_t lane, const uint32_t (&acc)[32])
+{
+    if (row0 >= p.m || col0 >= p.n)
+        return;
+    uint32_t packed[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i)
+        packed[i] = ptx::pack_bf16x2(acc[2 * i], acc[2 * i + 1]);
+
+    if (p.c_vec_ok && col0 + 32 <= p.n) {
+        const uint32_t row = row0 + lane;
+        if (row < p.m) {
+            uint4 *dst = reinterpret_cast<uint4 *>(p.c + static_cast<uint64_t>(row) * p.ldc + col0);
+#pragma unroll
+            for (int v = 0; v < 4; ++v)
+                dst[v] = make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
+        }
+        return;
+    }
+
+    uint4 *mine = reinterpret_cast<uint4 *>(stage_warp + lane * kStageRowBytes);
+#pragma unroll
+    for (int v = 0; v < 4; ++v)
+        mine[v] = make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
+    __syncwarp();
+    const uint32_t rows = min(32u, p.m - row0);
+    const bool col_ok = col0 + lane < p.n;
+    __nv_bfloat16 *dst = p.c + static_cast<uint64_t>(row0) * p.ldc + col0 + lane;
+    const uint8_t *src = stage_warp + lane * 2;
+    for (uint32_t r = 0; r < rows; ++r) {
+        const __nv_bfloat16 v = *reinterpret_cast<const __nv_bfloat16 *>(src + r * kStageRowBytes);
+        if (col_ok)
+            dst[static_cast<uint64_t>(r) * p.ldc] = v;
+    }
+    __syncwarp();
+}
+
+// Drain one 128-row x BN-column fp32 accumulator from TMEM to C.  Executed by the
+// four epilogue warps; `quarter` = warp index % 4 selects the 32 TMEM lanes the
+// warp may read; `tile_row0` / `tile_col0` locate the CTA's 128 x BN block in C.
+template <uint32_t BN>
+__device__ __forceinline__ void drain_accumulator(const GemmParams &p, uint8_t *stage_warp, uint32_t tmem_acc,
+                                                  uint32_t quarter, uint32_t lane, uint32_t tile_row0,
+                                                  uint32_t tile_col0)
+{
+    const uint32_t taddr = tmem_acc + ((quarter * 32u) << 16);
+    const uint32_t row0 = tile_row0 + quarter * 32u;
+#pragma unroll 1
+    for (uint32_t c = 0; c < BN / 32; ++c) {
+        uint32_t v[32];
+        ptx::tmem_ld_32x32b_x32(taddr + c * 32u, v);
+        ptx::tmem_ld_wait();
+        store_chunk(p, stage_warp, row0, tile_col0 + c * 32u, lane, v);
+    }
+}
+
+// One CTA waits on a barrier that nothing completes; exercises the bounded wait.
+__global__ void wait_expires_kernel(DeviceStatus *status, uint64_t budget_ns)
+{
+    __shared__ __align__(8) uint64_t bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        ptx::mbar_init(ptx::smem_u32(&bar), 1);
+        ptx::fence_barrier_init();
+        const WaitCtl ctl{&abort_flag, status, budget_ns};
+        (void)wait_bounded(ptx::smem_u32(&bar), 0, ctl, 9);
+    }
+}
+
+}  // namespace maize

@@ -25,77 +25,9 @@
 // the status word, every role falls through to the common teardown, in-flight
 // copies get time to land, TMEM is freed and the kernel returns.  Nothing traps.
 #pragma once
-#include "ptx_sm100.cuh"
+#include "gemm_common.cuh"
 
 namespace maize {
-
-constexpr int kStatusOk = 0;
-constexpr int kStatusTimeout = 4;      // == MAIZE_ERR_TIMEOUT
-constexpr int kStatusDeviceAbort = 5;  // == MAIZE_ERR_DEVICE_ABORT
-
-// Device status block: [0] worst status code, [1] role that gave up, [2] CTA, [3] spare.
-struct DeviceStatus {
-    int code;
-    int role;
-    int cta;
-    int detail;
-};
-
-constexpr uint32_t kBlockM = 128;  // rows of C per CTA tile = TMEM lanes = UMMA M
-constexpr uint32_t kBlockK = 64;   // bf16 elements per k-block = one 128-byte swizzle row
-constexpr uint32_t kUmmaK = 16;    // K per tcgen05.mma for 16-bit operands
-constexpr uint32_t kNumThreads = 192;
-constexpr uint32_t kNumEpilogueThreads = 128;
-
-struct WaitCtl {
-    volatile int *abort_flag;  // shared memory, CTA-wide
-    DeviceStatus *status;      // global memory
-    uint64_t budget_ns;
-};
-
-// Bounded wait on an mbarrier phase.  Returns false if the budget ran out or some
-// other role of this CTA already gave up.
-__device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity, const WaitCtl &ctl, int role)
-{
-    if (ptx::mbar_try_wait(bar, parity))
-        return true;
-    const uint64_t t0 = ptx::global_timer_ns();
-    for (uint32_t it = 1;; ++it) {
-        if (ptx::mbar_try_wait(bar, parity))
-            return true;
-        if ((it & 31u) == 0u) {
-            if (*ctl.abort_flag)
-                return false;
-            if (ptx::global_timer_ns() - t0 > ctl.budget_ns) {
-                *ctl.abort_flag = 1;
-                if (atomicMax(&ctl.status->code, kStatusTimeout) < kStatusTimeout) {
-                    ctl.status->role = role;
-                    ctl.status->cta = static_cast<int>(blockIdx.x);
-                }
-                return false;
-            }
-        }
-    }
-}
-
-// Tile order: groups of kGroupM row-blocks sweep all column-blocks, so that the
-// CTAs running at one time share A row panels and B column panels in L2.
-struct TileCoord {
-    uint32_t m_blk, n_blk;
-};
-
-__device__ __forceinline__ TileCoord tile_coord(uint32_t t, uint32_t tiles_m, uint32_t tiles_n, uint32_t group_m)
-{
-    const uint32_t per_group = group_m * tiles_n;
-    const uint32_t g = t / per_group;
-    const uint32_t first_m = g * group_m;
-    const uint32_t rows = min(tiles_m - first_m, group_m);
-    const uint32_t r = t - g * per_group;
-    TileCoord c;
-    c.m_blk = first_m + r % rows;
-    c.n_blk = r / rows;
-    return c;
-}
 
 template <uint32_t BN, uint32_t STAGES>
 struct GemmSmemLayout {
@@ -103,55 +35,21 @@ struct GemmSmemLayout {
     static constexpr uint32_t kBBytes = BN * kBlockK * 2;
     static constexpr uint32_t kStageBytes = kABytes + kBBytes;
     static constexpr uint32_t kRingBytes = STAGES * kStageBytes;
-    // after the ring: full[STAGES], empty[STAGES], acc_full[2], acc_empty[2], tmem slot, abort flag
-    static constexpr uint32_t kBarOffset = kRingBytes;
+    // after the ring: epilogue staging, then full[STAGES], empty[STAGES], acc_full[2], acc_empty[2],
+    // the TMEM base slot and the abort flag
+    static constexpr uint32_t kStagingOffset = kRingBytes;
+    static constexpr uint32_t kBarOffset = kStagingOffset + kStageBytesTotal;
     static constexpr uint32_t kNumBars = 2 * STAGES + 4;
     static constexpr uint32_t kTmemSlotOffset = kBarOffset + kNumBars * 8;
     static constexpr uint32_t kAbortOffset = kTmemSlotOffset + 4;
     static constexpr uint32_t kUsedBytes = kAbortOffset + 4;
     static constexpr uint32_t kDynamicBytes = kUsedBytes + 1024;  // slack for the 1024-byte alignment
     static_assert(kStageBytes % 1024 == 0, "stage bases must stay 1024-byte aligned for the 128B swizzle");
+    static_assert(kBarOffset % 16 == 0, "barriers need 8-byte, staging rows 16-byte alignment");
     static_assert(kDynamicBytes <= 232448, "exceeds 227 KiB of shared memory per CTA");
+    // one CTA per SM by construction, so the 2*BN TMEM columns never oversubscribe the SM's 512
+    static_assert(kDynamicBytes > 116224, "two CTAs could share an SM and contend for TMEM");
 };
-
-struct GemmParams {
-    __nv_bfloat16 *c;
-    uint64_t ldc;  // elements
-    uint32_t m, n, k;
-    uint32_t tiles_m, tiles_n;
-    uint32_t group_m;
-    uint32_t c_vec_ok;  // 1: C rows start 16-byte aligned (ldc % 8 == 0 and base aligned)
-    DeviceStatus *status;
-    uint64_t timeout_ns;
-};
-
-// Convert 32 fp32 accumulators of one C row to bf16 and store columns [col0, col0+32) ∩ [0, n).
-__device__ __forceinline__ void store_row_chunk(const GemmParams &p, uint32_t row, uint32_t col0,
-                                                const uint32_t (&acc)[32])
-{
-    if (row >= p.m || col0 >= p.n)
-        return;
-    __nv_bfloat16 *dst = p.c + static_cast<uint64_t>(row) * p.ldc + col0;
-    if (p.c_vec_ok && col0 + 32 <= p.n) {
-        uint4 *dst4 = reinterpret_cast<uint4 *>(dst);
-#pragma unroll
-        for (int v = 0; v < 4; ++v) {
-            uint4 q;
-            q.x = ptx::pack_bf16x2(acc[8 * v + 0], acc[8 * v + 1]);
-            q.y = ptx::pack_bf16x2(acc[8 * v + 2], acc[8 * v + 3]);
-            q.z = ptx::pack_bf16x2(acc[8 * v + 4], acc[8 * v + 5]);
-            q.w = ptx::pack_bf16x2(acc[8 * v + 6], acc[8 * v + 7]);
-            dst4[v] = q;
-        }
-    } else {
-        const uint32_t valid = min(32u, p.n - col0);
-#pragma unroll
-        for (uint32_t j = 0; j < 32; ++j) {
-            if (j < valid)
-                dst[j] = __float2bfloat16_rn(__uint_as_float(acc[j]));
-        }
-    }
-}
 
 template <uint32_t BN, uint32_t STAGES>
 __global__ void __launch_bounds__(kNumThreads, 1)
@@ -181,6 +79,9 @@ gemm_bf16_sm100_1cta(const __grid_constant__ CUtensorMap tma_a, const __grid_con
     const uint32_t num_tiles = p.tiles_m * p.tiles_n;
     const uint32_t num_kb = (p.k + kBlockK - 1) / kBlockK;
     const WaitCtl ctl{abort_flag, p.status, p.timeout_ns};
+    const bool prof = p.profile != nullptr;
+    unsigned long long *prof_out = prof ? p.profile + static_cast<size_t>(blockIdx.x) * kProfileSlots : nullptr;
+    const long long t_start = prof ? ptx::sm_clock64() : 0;
 
     if (threadIdx.x == 0) {
         ptx::prefetch_tensormap(&tma_a);
@@ -210,24 +111,35 @@ gemm_bf16_sm100_1cta(const __grid_constant__ CUtensorMap tma_a, const __grid_con
         if (lane == 0) {
             uint32_t stage = 0, phase = 0;
             bool ok = true;
+            unsigned long long w_empty = 0;
             for (uint32_t t = blockIdx.x; ok && t < num_tiles; t += gridDim.x) {
                 const TileCoord tc = tile_coord(t, p.tiles_m, p.tiles_n, p.group_m);
-                const int32_t m0 = static_cast<int32_t>(tc.m_blk * kBlockM);
-                const int32_t n0 = static_cast<int32_t>(tc.n_blk * BN);
+                const bool hot = (p.debug_flags & 1u) != 0u;
+                const int32_t m0 = hot ? 0 : static_cast<int32_t>(tc.m_blk * kBlockM);
+                const int32_t n0 = hot ? 0 : static_cast<int32_t>(tc.n_blk * BN);
                 for (uint32_t kb = 0; kb < num_kb; ++kb) {
-                    if (!(ok = wait_bounded(empty_bar(stage), phase ^ 1u, ctl, 1)))
+                    WaitTimer wt(prof);
+                    ok = wait_bounded(empty_bar(stage), phase ^ 1u, ctl, 1);
+                    wt.stop(w_empty);
+                    if (!ok)
                         break;
                     const uint32_t sa = smem_base + stage * L::kStageBytes;
                     const uint32_t sb = sa + L::kABytes;
-                    ptx::mbar_arrive_expect_tx(full_bar(stage), L::kStageBytes);
-                    ptx::tma_load_2d(sa, &tma_a, full_bar(stage), static_cast<int32_t>(kb * kBlockK), m0);
-                    ptx::tma_load_2d(sb, &tma_b, full_bar(stage), static_cast<int32_t>(kb * kBlockK), n0);
+                    if (p.debug_flags & 2u) {
+                        ptx::mbar_arrive(full_bar(stage));
+                    } else {
+                        ptx::mbar_arrive_expect_tx(full_bar(stage), L::kStageBytes);
+                        ptx::tma_load_2d(sa, &tma_a, full_bar(stage), static_cast<int32_t>(kb * kBlockK), m0);
+                        ptx::tma_load_2d(sb, &tma_b, full_bar(stage), static_cast<int32_t>(kb * kBlockK), n0);
+                    }
                     if (++stage == STAGES) {
                         stage = 0;
                         phase ^= 1u;
                     }
                 }
             }
+            if (prof)
+                prof_out[kProfProducerWaitEmpty] = w_empty;
         }
         __syncwarp();
     } else if (warp == 1) {
@@ -236,13 +148,24 @@ gemm_bf16_sm100_1cta(const __grid_constant__ CUtensorMap tma_a, const __grid_con
             uint32_t stage = 0, phase = 0;
             uint32_t acc = 0, acc_phase = 0;
             bool ok = true;
+            unsigned long long w_full = 0, w_acc = 0;
             for (uint32_t t = blockIdx.x; ok && t < num_tiles; t += gridDim.x) {
-                if (!(ok = wait_bounded(acc_empty_bar(acc), acc_phase ^ 1u, ctl, 2)))
+                {
+                    WaitTimer wt(prof);
+                    ok = wait_bounded(acc_empty_bar(acc), acc_phase ^ 1u, ctl, 2);
+                    wt.stop(w_acc);
+                }
+                if (!ok)
                     break;
                 ptx::tcgen05_fence_after();
                 const uint32_t tmem_d = tmem_base + acc * BN;
                 for (uint32_t kb = 0; kb < num_kb; ++kb) {
-                    if (!(ok = wait_bounded(full_bar(stage), phase, ctl, 2)))
+                    {
+                        WaitTimer wt(prof);
+                        ok = wait_bounded(full_bar(stage), phase, ctl, 2);
+                        wt.stop(w_full);
+                    }
+                    if (!ok)
                         break;
                     ptx::tcgen05_fence_after();
                     const uint32_t sa = smem_base + stage * L::kStageBytes;
@@ -267,31 +190,36 @@ gemm_bf16_sm100_1cta(const __grid_constant__ CUtensorMap tma_a, const __grid_con
                     acc_phase ^= 1u;
                 }
             }
+            if (prof) {
+                prof_out[kProfMmaWaitFull] = w_full;
+                prof_out[kProfMmaWaitAccEmpty] = w_acc;
+            }
         }
         __syncwarp();
     } else {
         // ----------------------------------------------------------- epilogue --
         const uint32_t quarter = warp & 3u;  // TMEM lanes this warp may read
+        uint8_t *stage_warp = smem_gen + L::kStagingOffset + (warp - 2u) * kStageWarpBytes;
         uint32_t acc = 0, acc_phase = 0;
         bool ok = true;
+        unsigned long long w_accfull = 0, w_drain = 0, n_tiles_done = 0;
         for (uint32_t t = blockIdx.x; ok && t < num_tiles; t += gridDim.x) {
             const TileCoord tc = tile_coord(t, p.tiles_m, p.tiles_n, p.group_m);
-            const uint32_t row = tc.m_blk * kBlockM + quarter * 32u + lane;
-            const uint32_t n0 = tc.n_blk * BN;
-            ok = wait_bounded(acc_full_bar(acc), acc_phase, ctl, 3);
+            {
+                WaitTimer wt(prof);
+                ok = wait_bounded(acc_full_bar(acc), acc_phase, ctl, 3);
+                wt.stop(w_accfull);
+            }
             // keep the warp converged for the .sync.aligned TMEM loads
             ok = __all_sync(0xffffffffu, ok);
             if (!ok)
                 break;
             ptx::tcgen05_fence_after();
-            const uint32_t taddr = tmem_base + ((quarter * 32u) << 16) + acc * BN;
-#pragma unroll 1
-            for (uint32_t c = 0; c < BN / 32; ++c) {
-                uint32_t v[32];
-                ptx::tmem_ld_32x32b_x32(taddr + c * 32u, v);
-                ptx::tmem_ld_wait();
-                store_row_chunk(p, row, n0 + c * 32u, v);
-            }
+            WaitTimer dt(prof);
+            drain_accumulator<BN>(p, stage_warp, tmem_base + acc * BN, quarter, lane, tc.m_blk * kBlockM,
+                                  tc.n_blk * BN);
+            dt.stop(w_drain);
+            ++n_tiles_done;
             ptx::tcgen05_fence_before();
             ptx::mbar_arrive(acc_empty_bar(acc));
             if (++acc == 2) {
@@ -299,11 +227,18 @@ gemm_bf16_sm100_1cta(const __grid_constant__ CUtensorMap tma_a, const __grid_con
                 acc_phase ^= 1u;
             }
         }
+        if (prof && warp == 2 && lane == 0) {
+            prof_out[kProfEpilogueWaitAccFull] = w_accfull;
+            prof_out[kProfEpilogueDrain] = w_drain;
+            prof_out[kProfTiles] = n_tiles_done;
+        }
     }
 
     // ---------------------------------------------------------------- teardown --
     ptx::tcgen05_fence_before();
     __syncthreads();
+    if (prof && threadIdx.x == 0)
+        prof_out[kProfCtaCycles] = static_cast<unsigned long long>(ptx::sm_clock64() - t_start);
     if (warp == 1) {
         if (*abort_flag) {
             // A role gave up: let TMA copies and MMAs still in flight finish before
@@ -313,20 +248,6 @@ gemm_bf16_sm100_1cta(const __grid_constant__ CUtensorMap tma_a, const __grid_con
         }
         ptx::tcgen05_fence_after();
         ptx::tmem_dealloc_1cta(tmem_base, kTmemCols);
-    }
-}
-
-// One CTA waits on a barrier that nothing completes; exercises the bounded wait.
-__global__ void wait_expires_kernel(DeviceStatus *status, uint64_t budget_ns)
-{
-    __shared__ __align__(8) uint64_t bar;
-    __shared__ int abort_flag;
-    if (threadIdx.x == 0) {
-        abort_flag = 0;
-        ptx::mbar_init(ptx::smem_u32(&bar), 1);
-        ptx::fence_barrier_init();
-        const WaitCtl ctl{&abort_flag, status, budget_ns};
-        (void)wait_bounded(ptx::smem_u32(&bar), 0, ctl, 9);
     }
 }
 

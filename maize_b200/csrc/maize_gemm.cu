@@ -14,6 +14,8 @@
 #include <string>
 
 #include "gemm_sm100.cuh"
+#include "gemm_sm100_2cta.cuh"
+#include "gemm_sm100_skinny.cuh"
 
 namespace {
 
@@ -26,18 +28,34 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t
 
 struct KernelVariant {
     const char *name;
+    uint32_t block_m;  // rows of C per tile (per CTA pair for the 2-CTA kernel)
     uint32_t block_n;
-    uint32_t stages;
+    uint32_t box_rows_b;  // rows of B one TMA box brings in
+    uint32_t ctas_per_tile;
 };
 
 // Index + 1 is the public kernel id.
 const KernelVariant kVariants[] = {
-    {"sm100_1cta_128x256x64_s4", 256, 4},
-    {"sm100_1cta_128x128x64_s6", 128, 6},
-    {"sm100_1cta_128x64x64_s8", 64, 8},
-    {"sm100_1cta_128x32x64_s8", 32, 8},
+    {"sm100_1cta_128x256x64_s4", 128, 256, 256, 1},
+    {"sm100_1cta_128x128x64_s6", 128, 128, 128, 1},
+    {"sm100_1cta_128x64x64_s8", 128, 64, 64, 1},
+    {"sm100_1cta_128x32x64_s8", 128, 32, 32, 1},
+    {"sm100_2cta_256x256x64_s6", 256, 256, 128, 2},
+    // skinny-M kernels: block_m = the MMA's N side (rows of A it can take), block_n = rows of B per tile
+    {"sm100_skinny_m16_128x64_s10", 16, 128, 128, 1},
+    {"sm100_skinny_m32_128x64_s9", 32, 128, 128, 1},
+    {"sm100_skinny_m64_128x64_s8", 64, 128, 128, 1},
+    {"sm100_skinny_m128_128x64_s6", 128, 128, 128, 1},
+    {"sm100_skinny_m16_128x128_s5", 16, 128, 128, 1},
+    {"sm100_skinny_m32_128x128_s5", 32, 128, 128, 1},
+    {"sm100_skinny_m64_128x128_s4", 64, 128, 128, 1},
 };
+constexpr int kFirstSkinny = 5;  // indices of the skinny variants
+constexpr int kLastSkinny = 11;
 constexpr int kNumVariants = static_cast<int>(sizeof(kVariants) / sizeof(kVariants[0]));
+constexpr int kMaxProfileCtas = 1024;
+constexpr size_t kPartialsBytes = size_t(32) << 20;  // stream-K scratch per context
+constexpr uint32_t kMaxSkinnyTiles = 65536;          // 4 counters each; N up to 8M rows
 
 class DeviceGuard {
 public:
@@ -68,11 +86,16 @@ struct maize_ctx {
     uint64_t timeout_ns = 2000000000ull;
     int force_kernel = 0;
     int max_ctas = 0;
+    uint32_t debug_flags = 0;
     uint64_t launches = 0;
     EncodeTiledFn encode = nullptr;
     void *staging = nullptr;  // device staging for the *_host entry point
     size_t staging_bytes = 0;
     bool attr_set[kNumVariants] = {};
+    float *d_partials = nullptr;        // stream-K scratch of the skinny kernels
+    unsigned int *d_counters = nullptr;  // arrival counters, zero between launches
+    unsigned long long *d_profile = nullptr;  // kProfileSlots counters per CTA, allocated when "profile" is set
+    int profile_ctas = 0;                      // CTAs of the last profiled launch
     std::string err;
 };
 
@@ -111,24 +134,31 @@ maize_status_t make_operand_map(maize_ctx_t *ctx, CUtensorMap *map, const void *
     return MAIZE_OK;
 }
 
-template <uint32_t BN, uint32_t STAGES>
-maize_status_t launch_variant(maize_ctx_t *ctx, int variant_index, const CUtensorMap &ta, const CUtensorMap &tb,
-                              const GemmParams &p, uint32_t grid, cudaStream_t stream)
+template <typename Kernel>
+maize_status_t launch_kernel(maize_ctx_t *ctx, int variant_index, Kernel kernel, uint32_t smem_bytes,
+                             const CUtensorMap &ta, const CUtensorMap &tb, const GemmParams &p, uint32_t grid,
+                             cudaStream_t stream)
 {
-    using L = maize::GemmSmemLayout<BN, STAGES>;
-    auto kernel = maize::gemm_bf16_sm100_1cta<BN, STAGES>;
     if (!ctx->attr_set[variant_index]) {
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes);
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
         if (e != cudaSuccess)
             return fail_cuda(ctx, "cudaFuncSetAttribute(max dynamic smem)", e);
         ctx->attr_set[variant_index] = true;
     }
-    kernel<<<grid, maize::kNumThreads, L::kDynamicBytes, stream>>>(ta, tb, p);
+    kernel<<<grid, maize::kNumThreads, smem_bytes, stream>>>(ta, tb, p);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess)
         return fail_cuda(ctx, "kernel launch", e);
     ctx->launches += 1;
     return MAIZE_OK;
+}
+
+template <uint32_t BN, uint32_t STAGES>
+maize_status_t launch_variant(maize_ctx_t *ctx, int variant_index, const CUtensorMap &ta, const CUtensorMap &tb,
+                              const GemmParams &p, uint32_t grid, cudaStream_t stream)
+{
+    return launch_kernel(ctx, variant_index, maize::gemm_bf16_sm100_1cta<BN, STAGES>,
+                         maize::GemmSmemLayout<BN, STAGES>::kDynamicBytes, ta, tb, p, grid, stream);
 }
 
 int pick_variant(const maize_ctx_t *ctx, uint32_t m, uint32_t n, uint32_t k)
@@ -138,6 +168,15 @@ int pick_variant(const maize_ctx_t *ctx, uint32_t m, uint32_t n, uint32_t k)
         return ctx->force_kernel - 1;
     const uint32_t sms = ctx ? static_cast<uint32_t>(ctx->sm_count) : 148u;
     const uint64_t tiles_m = (m + maize::kBlockM - 1) / maize::kBlockM;
+    // One row-block of A or less: the shape is bound by streaming B, take the stream-K kernels.
+    if (m <= 16)
+        return kFirstSkinny;
+    if (m <= 32)
+        return kFirstSkinny + 1;
+    if (m <= 64)
+        return kFirstSkinny + 2;
+    if (m <= 128 && (uint64_t(n) + 255) / 256 < 2ull * sms)
+        return kFirstSkinny + 3;
     // Widest tile whose tile count still fills the machine reasonably; narrow N gets narrow tiles.
     if (n <= 32)
         return 3;
@@ -156,6 +195,44 @@ int pick_variant(const maize_ctx_t *ctx, uint32_t m, uint32_t n, uint32_t k)
     if (tiles128 >= sms || n > 64)
         return 1;
     return 2;
+}
+
+template <uint32_t MMA_N, uint32_t KBS, uint32_t STAGES>
+maize_status_t launch_skinny(maize_ctx_t *ctx, int vi, const CUtensorMap &tw, const CUtensorMap &tx,
+                             maize::SkinnyParams p, cudaStream_t stream)
+{
+    using L = maize::SkinnySmemLayout<MMA_N, KBS, STAGES>;
+    auto kernel = maize::gemm_bf16_sm100_skinny<MMA_N, KBS, STAGES>;
+    p.num_kb = (p.k + maize::kBlockK * KBS - 1) / (maize::kBlockK * KBS);
+    if (!ctx->attr_set[vi]) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes);
+        if (e != cudaSuccess)
+            return fail_cuda(ctx, "cudaFuncSetAttribute(max dynamic smem)", e);
+        ctx->attr_set[vi] = true;
+    }
+    // Equal contiguous unit ranges per CTA; fall back to whole tiles per CTA when the scratch cannot hold
+    // the partials, or when there is so much work that whole tiles balance within a few percent anyway.
+    uint32_t cap = static_cast<uint32_t>(ctx->sm_count);
+    if (ctx->max_ctas > 0 && static_cast<uint32_t>(ctx->max_ctas) < cap)
+        cap = static_cast<uint32_t>(ctx->max_ctas);
+    const uint64_t units = uint64_t(p.tiles_n) * p.num_kb;
+    uint64_t q = (units + cap - 1) / cap;
+    auto parts_bound = [&](uint64_t per_cta) { return (p.num_kb - 1 + per_cta - 1) / per_cta + 1; };
+    const size_t slot_bytes = size_t(MMA_N) * 128 * sizeof(float);
+    const bool plenty = p.tiles_n >= 8ull * cap;
+    if (plenty || p.tiles_n > kMaxSkinnyTiles || size_t(p.tiles_n) * parts_bound(q) * slot_bytes > kPartialsBytes)
+        q = ((q + p.num_kb - 1) / p.num_kb) * p.num_kb;  // whole tiles: every tile has one part
+    if (q > 0xffffffffull)
+        return fail(ctx, MAIZE_ERR_UNSUPPORTED, "problem too large for the skinny kernel");
+    p.units_per_cta = static_cast<uint32_t>(q);
+    p.max_parts = (q % p.num_kb == 0) ? 1u : static_cast<uint32_t>(parts_bound(q));
+    const uint32_t grid = static_cast<uint32_t>((units + q - 1) / q);
+    kernel<<<grid, maize::kNumThreads, L::kDynamicBytes, stream>>>(tw, tx, p);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess)
+        return fail_cuda(ctx, "kernel launch", e);
+    ctx->launches += 1;
+    return MAIZE_OK;
 }
 
 maize_status_t gemm_impl(maize_ctx_t *ctx, const void *a, uint64_t lda, const void *b, uint64_t ldb, void *c,
@@ -192,11 +269,46 @@ maize_status_t gemm_impl(maize_ctx_t *ctx, const void *a, uint64_t lda, const vo
     const int vi = pick_variant(ctx, m, n, k);
     const KernelVariant &kv = kVariants[vi];
 
+    if (vi >= kFirstSkinny && vi <= kLastSkinny) {
+        if (m > kv.block_m)
+            return fail(ctx, MAIZE_ERR_UNSUPPORTED, "forced skinny kernel takes fewer rows of A than M");
+        CUtensorMap tw, tx;
+        maize_status_t sst = make_operand_map(ctx, &tw, b, n, k, ldb, maize::kSkinnyTileN);
+        if (sst != MAIZE_OK)
+            return sst;
+        sst = make_operand_map(ctx, &tx, a, m, k, lda, kv.block_m);
+        if (sst != MAIZE_OK)
+            return sst;
+        maize::SkinnyParams sp;
+        sp.c = static_cast<__nv_bfloat16 *>(c);
+        sp.ldc = ldc;
+        sp.m = m;
+        sp.n = n;
+        sp.k = k;
+        sp.tiles_n = (n + maize::kSkinnyTileN - 1) / maize::kSkinnyTileN;
+        sp.num_kb = (k + maize::kBlockK - 1) / maize::kBlockK;
+        sp.units_per_cta = 0;
+        sp.max_parts = 1;
+        sp.partials = ctx->d_partials;
+        sp.counters = ctx->d_counters;
+        sp.status = ctx->d_status;
+        sp.timeout_ns = ctx->timeout_ns;
+        switch (vi - kFirstSkinny) {
+        case 0: return launch_skinny<16, 1, 10>(ctx, vi, tw, tx, sp, stream);
+        case 1: return launch_skinny<32, 1, 9>(ctx, vi, tw, tx, sp, stream);
+        case 2: return launch_skinny<64, 1, 8>(ctx, vi, tw, tx, sp, stream);
+        case 3: return launch_skinny<128, 1, 6>(ctx, vi, tw, tx, sp, stream);
+        case 4: return launch_skinny<16, 2, 5>(ctx, vi, tw, tx, sp, stream);
+        case 5: return launch_skinny<32, 2, 5>(ctx, vi, tw, tx, sp, stream);
+        default: return launch_skinny<64, 2, 4>(ctx, vi, tw, tx, sp, stream);
+        }
+    }
+
     CUtensorMap ta, tb;
     maize_status_t st = make_operand_map(ctx, &ta, a, m, k, lda, maize::kBlockM);
     if (st != MAIZE_OK)
         return st;
-    st = make_operand_map(ctx, &tb, b, n, k, ldb, kv.block_n);
+    st = make_operand_map(ctx, &tb, b, n, k, ldb, kv.box_rows_b);
     if (st != MAIZE_OK)
         return st;
 
@@ -206,25 +318,37 @@ maize_status_t gemm_impl(maize_ctx_t *ctx, const void *a, uint64_t lda, const vo
     p.m = m;
     p.n = n;
     p.k = k;
-    p.tiles_m = (m + maize::kBlockM - 1) / maize::kBlockM;
+    p.tiles_m = (m + kv.block_m - 1) / kv.block_m;
     p.tiles_n = (n + kv.block_n - 1) / kv.block_n;
-    p.group_m = 16;
+    p.group_m = 2048 / kv.block_m;  // row-blocks swept together: 2048 rows of A stay hot in L2
     p.c_vec_ok = (ldc % 8 == 0 && reinterpret_cast<uintptr_t>(c) % 16 == 0) ? 1u : 0u;
     p.status = ctx->d_status;
     p.timeout_ns = ctx->timeout_ns;
+    p.profile = ctx->d_profile;
+    p.debug_flags = ctx->debug_flags;
     const uint64_t tiles = uint64_t(p.tiles_m) * p.tiles_n;
     if (tiles > 0x7fffffffull)
         return fail(ctx, MAIZE_ERR_UNSUPPORTED, "too many output tiles");
     uint32_t cap = static_cast<uint32_t>(ctx->sm_count);
     if (ctx->max_ctas > 0 && static_cast<uint32_t>(ctx->max_ctas) < cap)
         cap = static_cast<uint32_t>(ctx->max_ctas);
-    const uint32_t grid = tiles < cap ? static_cast<uint32_t>(tiles) : cap;
+    cap /= kv.ctas_per_tile;  // tiles (CTAs or CTA pairs) in flight
+    if (cap == 0)
+        cap = 1;
+    const uint32_t grid = (tiles < cap ? static_cast<uint32_t>(tiles) : cap) * kv.ctas_per_tile;
+    if (ctx->d_profile) {
+        ctx->profile_ctas = static_cast<int>(grid);
+        cudaMemsetAsync(ctx->d_profile, 0, sizeof(unsigned long long) * maize::kProfileSlots * kMaxProfileCtas, stream);
+    }
 
     switch (vi) {
     case 0: return launch_variant<256, 4>(ctx, vi, ta, tb, p, grid, stream);
     case 1: return launch_variant<128, 6>(ctx, vi, ta, tb, p, grid, stream);
     case 2: return launch_variant<64, 8>(ctx, vi, ta, tb, p, grid, stream);
-    default: return launch_variant<32, 8>(ctx, vi, ta, tb, p, grid, stream);
+    case 3: return launch_variant<32, 8>(ctx, vi, ta, tb, p, grid, stream);
+    default:
+        return launch_kernel(ctx, vi, maize::gemm_bf16_sm100_2cta<256, 6>, maize::PairSmemLayout<256, 6>::kDynamicBytes,
+                             ta, tb, p, grid, stream);
     }
 }
 
@@ -287,6 +411,9 @@ maize_status_t maize_ctx_create(int device, maize_ctx_t **out)
     ctx->encode = reinterpret_cast<EncodeTiledFn>(fn);
     if (cudaMalloc(&ctx->d_status, sizeof(DeviceStatus)) != cudaSuccess ||
         cudaMemset(ctx->d_status, 0, sizeof(DeviceStatus)) != cudaSuccess ||
+        cudaMalloc(&ctx->d_partials, kPartialsBytes) != cudaSuccess ||
+        cudaMalloc(&ctx->d_counters, sizeof(unsigned int) * 4 * kMaxSkinnyTiles) != cudaSuccess ||
+        cudaMemset(ctx->d_counters, 0, sizeof(unsigned int) * 4 * kMaxSkinnyTiles) != cudaSuccess ||
         cudaMallocHost(&ctx->h_status, sizeof(DeviceStatus)) != cudaSuccess) {
         maize_ctx_destroy(ctx);
         return MAIZE_ERR_CUDA;
@@ -306,6 +433,12 @@ void maize_ctx_destroy(maize_ctx_t *ctx)
         cudaFreeHost(ctx->h_status);
     if (ctx->staging)
         cudaFree(ctx->staging);
+    if (ctx->d_profile)
+        cudaFree(ctx->d_profile);
+    if (ctx->d_partials)
+        cudaFree(ctx->d_partials);
+    if (ctx->d_counters)
+        cudaFree(ctx->d_counters);
     delete ctx;
 }
 
@@ -425,6 +558,20 @@ maize_status_t maize_ctx_set(maize_ctx_t *ctx, const char *key, int64_t value)
         if (value < 0 || value > kNumVariants)
             return fail(ctx, MAIZE_ERR_INVALID_ARG, "force_kernel out of range");
         ctx->force_kernel = static_cast<int>(value);
+    } else if (!strcmp(key, "profile")) {
+        // per-CTA cycle accounting of the next launches (a debugging aid; costs a few clock reads per wait)
+        DeviceGuard guard(ctx->device);
+        if (value && !ctx->d_profile) {
+            cudaError_t e = cudaMalloc(&ctx->d_profile, sizeof(unsigned long long) * maize::kProfileSlots * kMaxProfileCtas);
+            if (e != cudaSuccess)
+                return fail_cuda(ctx, "cudaMalloc(profile)", e);
+        } else if (!value && ctx->d_profile) {
+            cudaDeviceSynchronize();
+            cudaFree(ctx->d_profile);
+            ctx->d_profile = nullptr;
+        }
+    } else if (!strcmp(key, "debug_flags")) {
+        ctx->debug_flags = static_cast<uint32_t>(value);
     } else if (!strcmp(key, "max_ctas")) {
         if (value < 0)
             return fail(ctx, MAIZE_ERR_INVALID_ARG, "max_ctas must be >= 0");
@@ -464,6 +611,22 @@ const char *maize_kernel_name(int id)
 int maize_pick_kernel(const maize_ctx_t *ctx, uint32_t m, uint32_t n, uint32_t k) { return pick_variant(ctx, m, n, k) + 1; }
 
 uint64_t maize_ctx_launch_count(const maize_ctx_t *ctx) { return ctx ? ctx->launches : 0; }
+
+int maize_ctx_read_profile(maize_ctx_t *ctx, uint64_t *out, int max_ctas, void *cuda_stream)
+{
+    if (!ctx || !out || !ctx->d_profile || max_ctas <= 0)
+        return 0;
+    DeviceGuard guard(ctx->device);
+    int n = ctx->profile_ctas < max_ctas ? ctx->profile_ctas : max_ctas;
+    if (n > kMaxProfileCtas)
+        n = kMaxProfileCtas;
+    cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+    if (cudaStreamSynchronize(stream) != cudaSuccess)
+        return 0;
+    if (cudaMemcpy(out, ctx->d_profile, sizeof(uint64_t) * maize::kProfileSlots * n, cudaMemcpyDeviceToHost) != cudaSuccess)
+        return 0;
+    return n;
+}
 
 maize_status_t maize_debug_wait_expires(maize_ctx_t *ctx, uint64_t budget_ns, void *cuda_stream)
 {

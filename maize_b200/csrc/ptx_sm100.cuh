@@ -1,5 +1,5 @@
 // Inline-PTX wrappers for the sm_100a features the GEMM kernels use: mbarrier,
-// TMA (cp.async.bulk.tensor, never with cluster multicast), tcgen05 MMA / TMEM.
+// TMA tiled loads and stores (every CTA issues its own), tcgen05 MMA / TMEM.
 //
 // These take the place of the instruction emitters the reference drives through
 // LLVM: cp.async + commit/wait groups (crates/maize_core/src/intrinsics/cuda/cp_async.rs:54-65),
@@ -29,6 +29,13 @@ __device__ __forceinline__ uint64_t global_timer_ns()
 {
     uint64_t t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+__device__ __forceinline__ long long sm_clock64()
+{
+    long long t;
+    asm volatile("mov.u64 %0, %%clock64;" : "=l"(t));
     return t;
 }
 
@@ -135,6 +142,31 @@ __device__ __forceinline__ void tma_load_2d_hint(uint32_t smem_dst, const CUtens
         " [%0], [%1, {%3, %4}], [%2], %5;" ::"r"(smem_dst),
         "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y), "l"(policy)
         : "memory");
+}
+
+// CTA-pair form of the tiled load: the data lands in THIS CTA's shared memory, the
+// completion bytes are signalled on `bar_cluster_addr`, a shared::cluster address
+// that may name the barrier of either CTA of the pair (every CTA issues its own
+// loads; none is shared between CTAs).
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t smem_dst, const CUtensorMap *map, uint32_t bar_cluster_addr,
+                                                 int32_t x, int32_t y)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4}], [%2];" ::"r"(smem_dst),
+        "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster_addr), "r"(x), "r"(y)
+        : "memory");
+}
+
+// Arrive (release, cluster scope) on a barrier named by a shared::cluster address.
+__device__ __forceinline__ void mbar_arrive_cluster_addr(uint32_t bar_cluster_addr)
+{
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster_addr) : "memory");
+}
+
+__device__ __forceinline__ void st_shared_cluster_u32(uint32_t cluster_addr, uint32_t value)
+{
+    asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(value) : "memory");
 }
 
 __device__ __forceinline__ uint64_t policy_evict_first()

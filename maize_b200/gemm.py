@@ -147,6 +147,15 @@ class Context:
         self.gemm_ld(a.data_ptr(), lda, b.data_ptr(), ldb, out.data_ptr(), ldc, m, n, k, stream)
         return out
 
+    PROFILE_SLOTS = ("producer_wait_empty", "mma_wait_full", "mma_wait_acc_empty", "epilogue_wait_acc_full",
+                     "epilogue_drain", "cta_cycles", "tiles", "spare")
+
+    def read_profile(self, stream=None):
+        """Per-CTA cycle counters of the last launch (after ``set("profile", 1)``): list of dicts."""
+        buf = (ctypes.c_uint64 * (8 * 1024))()
+        n = self._lib.maize_ctx_read_profile(self._h, buf, 1024, _stream_handle(stream))
+        return [dict(zip(self.PROFILE_SLOTS, buf[8 * i:8 * i + 8])) for i in range(n)]
+
     def debug_wait_expires(self, budget_ns: int, stream=None) -> None:
         self._check(self._lib.maize_debug_wait_expires(self._h, int(budget_ns), _stream_handle(stream)))
 

@@ -34,18 +34,18 @@ def test_bounded_wait_returns_timeout(ctx):
     ctx.poll()  # the status word was cleared
 
 
-@pytest.mark.parametrize("force", [1, 2, 3, 4])
+@pytest.mark.parametrize("force", [1, 2, 3, 4, 5])
 def test_single_tile_single_kblock(ctx, oracle, force):
     run_case(ctx, oracle, 128, 256, 64, seed=10, force=force)
 
 
-@pytest.mark.parametrize("force", [1, 2, 3, 4])
+@pytest.mark.parametrize("force", [1, 2, 3, 4, 5])
 def test_ring_wraps(ctx, oracle, force):
     # more k-blocks than stages: every barrier changes phase several times
     run_case(ctx, oracle, 128, 256, 64 * 21, seed=11, force=force)
 
 
-@pytest.mark.parametrize("force", [1, 2, 3, 4])
+@pytest.mark.parametrize("force", [1, 2, 3, 4, 5])
 def test_many_tiles_per_cta(ctx, oracle, force):
     # more tiles than SMs for every variant: both TMEM accumulator buffers and their phases cycle
     run_case(ctx, oracle, 128 * 10, 256 * 9, 256, seed=12, force=force)
@@ -55,9 +55,52 @@ def test_many_tiles_per_cta(ctx, oracle, force):
     (1, 1, 8), (1, 8, 8), (7, 5, 16), (130, 250, 72), (127, 33, 520), (300, 1000, 136), (129, 257, 64),
     (128, 255, 128), (513, 77, 1032), (64, 4096, 256), (2000, 24, 512),
 ])
-@pytest.mark.parametrize("force", [0, 1, 2, 3, 4])
+@pytest.mark.parametrize("force", [0, 1, 2, 3, 4, 5])
 def test_ragged_edges(ctx, oracle, m, n, k, force):
     run_case(ctx, oracle, m, n, k, seed=13, force=force)
+
+
+@pytest.mark.parametrize("m,n,k", [
+    (1, 128, 64), (16, 128, 64), (16, 128, 640), (16, 4096, 1024), (13, 1000, 520), (3, 77, 72), (16, 16384, 256),
+    (32, 2048, 512), (20, 2050, 520), (64, 1024, 1024), (50, 999, 264), (128, 4096, 512), (100, 300, 136),
+    (16, 300000, 64), (8, 128 * 300, 4096),
+])
+def test_skinny_shapes(ctx, oracle, m, n, k):
+    """M <= 128 goes to the stream-K kernels: whole tiles, split tiles (2 and more parts), ragged N and K,
+    more tiles than SMs, and the whole-tile fallback for very many tiles."""
+    assert "skinny" in ctx.pick_kernel(m, n, k)
+    run_case(ctx, oracle, m, n, k, seed=19)
+    run_case(ctx, oracle, m, n, k, seed=20)  # again: the arrival counters were reset by the first launch
+
+
+@pytest.mark.parametrize("force", [6, 7, 8, 9, 10, 11, 12])
+def test_skinny_variants_forced(ctx, oracle, force):
+    run_case(ctx, oracle, 16, 128 * 37, 64 * 29, seed=21, force=force)
+    run_case(ctx, oracle, 5, 333, 200, seed=22, force=force)
+    run_case(ctx, oracle, 16, 128 * 150, 4104, seed=24, force=force)  # odd number of k-blocks, split tiles
+
+
+def test_skinny_is_deterministic(ctx, oracle):
+    import torch
+    a, b = make_inputs(oracle, 16, 16384, 4096, 23)
+    da, db = to_device(a), to_device(b)
+    outs = [ctx.gemm(da, db).clone() for _ in range(3)]
+    ctx.poll()
+    assert all(torch.equal(outs[0].view(torch.int16), o.view(torch.int16)) for o in outs[1:])
+
+
+def test_forced_skinny_rejects_tall_a(ctx):
+    import torch
+    import maize_b200
+    a = torch.zeros((64, 64), dtype=torch.bfloat16, device="cuda")
+    b = torch.zeros((128, 64), dtype=torch.bfloat16, device="cuda")
+    ctx.set("force_kernel", 6)
+    try:
+        with pytest.raises(maize_b200.MaizeError) as e:
+            ctx.gemm(a, b)
+        assert e.value.status == maize_b200._ffi.UNSUPPORTED
+    finally:
+        ctx.set("force_kernel", 0)
 
 
 def test_canaries_around_c(ctx, oracle):
@@ -161,10 +204,11 @@ def test_host_entry_point(ctx, oracle):
     assert np.array_equal(pc.numpy().view(np.uint16), c)
 
 
+@pytest.mark.parametrize("force", [0, 1, 5])
 @pytest.mark.parametrize("name", ["c1", "c2", "c3"])
-def test_baseline_configs_full(ctx, oracle, name):
+def test_baseline_configs_full(ctx, oracle, name, force):
     m, n, k, da, sa, db, sb, seed = CONFIGS[name]
-    run_case(ctx, oracle, m, n, k, seed=seed, dist_a=da, scale_a=sa, dist_b=db, scale_b=sb)
+    run_case(ctx, oracle, m, n, k, seed=seed, force=force, dist_a=da, scale_a=sa, dist_b=db, scale_b=sb)
 
 
 def test_deterministic_across_launches(ctx, oracle):
