@@ -1,21 +1,23 @@
 // CTA-pair (cta_group::2) variant of the persistent BF16 GEMM: two CTAs on the two
-// SMs of a TPC compute one 256 x BN tile of C together (BN = 256, or 128 for shapes
-// whose tile count would otherwise leave the last wave mostly empty).
+// SMs of a TPC compute one 256 x 256 tile of C together.
 //
 //   - CTA r of the pair (r = %cluster_ctarank, 0 = leader) owns rows r*128..r*128+127
 //     of the tile: it loads those 128 rows of A and ONE HALF (128 of 256 rows) of the
 //     B tile per k-block into its own shared memory, so each SM pulls 32 KiB per
-//     k-block instead of 48 KiB and the ring is 6 deep instead of 4.
+//     k-block instead of 48 KiB and the ring holds 6 k-blocks instead of 4.
 //   - Every CTA issues its own TMA loads (none is shared between CTAs); the peer's loads
 //     signal their bytes on the LEADER's full barrier, which expects both halves.
 //   - One thread of the leader issues tcgen05.mma.cta_group::2 (M = 256, N = 256,
 //     K = 16); the hardware reads A and B from both CTAs' shared memory at equal
 //     offsets and writes rows 0-127 of the accumulator to the leader's TMEM and
 //     rows 128-255 to the peer's.
-//   - Stage release and accumulator hand-over are two plain tcgen05.commit each:
-//     one on the leader's barrier, one on the peer's (address through mapa).
+//   - Stage release and accumulator hand-over are one tcgen05.commit each that
+//     arrives on the barrier of both CTAs (two separate commits, one per CTA, cost
+//     7% more cycles when measured).
 //   - Both CTAs drain their own 128 x 256 accumulator half; one lane per epilogue
 //     warp arrives on the leader's acc_empty barrier (8 arrivals per buffer).
+//   - KBS = k-blocks per ring stage (1 or 2): with 2 the leader commits once per
+//     eight MMAs instead of once per four.
 //
 // Role split, bounded waits and teardown follow the one-CTA kernel; a cluster
 // barrier brackets the body so that no CTA exits while its peer can still signal
@@ -27,11 +29,11 @@ namespace maize {
 
 constexpr uint32_t kPairBlockM = 256;
 
-template <uint32_t BN, uint32_t STAGES>
+template <uint32_t BN, uint32_t KBS, uint32_t STAGES>
 struct PairSmemLayout {
-    static constexpr uint32_t kABytes = kBlockM * kBlockK * 2;   // this CTA's 128 rows of A
-    static constexpr uint32_t kBBytes = (BN / 2) * kBlockK * 2;  // this CTA's half of the B tile
-    static constexpr uint32_t kStageBytes = kABytes + kBBytes;   // 32 KiB (BN = 256) or 24 KiB (BN = 128)
+    static constexpr uint32_t kABytes = kBlockM * kBlockK * 2;          // this CTA's 128 rows of A, one k-block
+    static constexpr uint32_t kBBytes = (BN / 2) * kBlockK * 2;         // this CTA's half of the B tile, one k-block
+    static constexpr uint32_t kStageBytes = KBS * (kABytes + kBBytes);  // [A0..A(KBS-1), B0..B(KBS-1)]
     static constexpr uint32_t kRingBytes = STAGES * kStageBytes;
     static constexpr uint32_t kStagingOffset = kRingBytes;
     static constexpr uint32_t kBarOffset = kStagingOffset + kStageBytesTotal;
@@ -45,15 +47,17 @@ struct PairSmemLayout {
     static_assert(kDynamicBytes > 116224, "two CTAs could share an SM and contend for TMEM");
 };
 
-template <uint32_t BN, uint32_t STAGES>
+template <uint32_t BN, uint32_t KBS, uint32_t STAGES>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNumThreads, 1)
 gemm_bf16_sm100_2cta(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                      const GemmParams p)
 {
-    using L = PairSmemLayout<BN, STAGES>;
-    static_assert(BN == 256 || BN == 128, "pair tile is 256 x 256 or 256 x 128");
+    using L = PairSmemLayout<BN, KBS, STAGES>;
+    static_assert(BN == 256, "pair tile is 256 x 256");
+    static_assert(KBS == 1 || KBS == 2, "one or two k-blocks per stage");
     constexpr uint32_t kTmemCols = 2 * BN;  // two BN-column accumulator buffers per CTA
     constexpr uint32_t kIdesc = ptx::make_instr_desc_bf16(kPairBlockM, BN);
+    constexpr uint32_t kStepK = KBS * kBlockK;
 
     extern __shared__ uint8_t smem_raw[];
     // Both CTAs of the pair see the same dynamic shared-memory base offset, so the aligned
@@ -75,7 +79,7 @@ gemm_bf16_sm100_2cta(const __grid_constant__ CUtensorMap tma_a, const __grid_con
     const uint32_t pair = blockIdx.x >> 1;
     const uint32_t num_pairs = gridDim.x >> 1;
     const uint32_t num_tiles = p.tiles_m * p.tiles_n;
-    const uint32_t num_kb = (p.k + kBlockK - 1) / kBlockK;
+    const uint32_t num_steps = (p.k + kStepK - 1) / kStepK;
     const WaitCtl ctl{abort_flag, p.status, p.timeout_ns};
     const bool prof = p.profile != nullptr;
     unsigned long long *prof_out = prof ? p.profile + static_cast<size_t>(blockIdx.x) * kProfileSlots : nullptr;
@@ -112,19 +116,23 @@ gemm_bf16_sm100_2cta(const __grid_constant__ CUtensorMap tma_a, const __grid_con
             uint32_t stage = 0, phase = 0;
             bool ok = true;
             unsigned long long w_empty = 0;
+            // L2 policy: the row panel of A is re-read by every column block of the sweep, B passes once
+            const bool hints = (p.debug_flags & 4u) != 0u;
+            const uint64_t pol_a = hints ? ptx::policy_evict_last() : ptx::policy_evict_normal();
+            const uint64_t pol_b = (p.debug_flags & 8u) ? ptx::policy_evict_first() : ptx::policy_evict_normal();
             for (uint32_t t = pair; ok && t < num_tiles; t += num_pairs) {
                 const TileCoord tc = tile_coord(t, p.tiles_m, p.tiles_n, p.group_m);
                 const bool hot = (p.debug_flags & 1u) != 0u;
                 const int32_t m0 = static_cast<int32_t>((hot ? 0 : tc.m_blk * kPairBlockM) + cta_rank * kBlockM);
                 const int32_t n0 = static_cast<int32_t>((hot ? 0 : tc.n_blk * BN) + cta_rank * (BN / 2));
-                for (uint32_t kb = 0; kb < num_kb; ++kb) {
+                for (uint32_t step = 0; step < num_steps; ++step) {
                     WaitTimer wt(prof);
                     ok = wait_bounded<true>(empty_bar(stage), phase ^ 1u, ctl, 1);
                     wt.stop(w_empty);
                     if (!ok)
                         break;
                     const uint32_t sa = smem_base + stage * L::kStageBytes;
-                    const uint32_t sb = sa + L::kABytes;
+                    const uint32_t sb = sa + KBS * L::kABytes;
                     const uint32_t leader_full = ptx::mapa_shared(full_bar(stage), 0);
                     if (p.debug_flags & 2u) {
                         if (cta_rank == 0)
@@ -132,8 +140,13 @@ gemm_bf16_sm100_2cta(const __grid_constant__ CUtensorMap tma_a, const __grid_con
                     } else {
                         if (cta_rank == 0)
                             ptx::mbar_arrive_expect_tx(full_bar(stage), 2 * L::kStageBytes);
-                        ptx::tma_load_2d_pair(sa, &tma_a, leader_full, static_cast<int32_t>(kb * kBlockK), m0);
-                        ptx::tma_load_2d_pair(sb, &tma_b, leader_full, static_cast<int32_t>(kb * kBlockK), n0);
+#pragma unroll
+                        for (uint32_t sub = 0; sub < KBS; ++sub) {
+                            // a k-block past the end of K is fetched all the same: TMA fills it with zeros
+                            const int32_t kx = static_cast<int32_t>((step * KBS + sub) * kBlockK);
+                            ptx::tma_load_2d_pair_hint(sa + sub * L::kABytes, &tma_a, leader_full, kx, m0, pol_a);
+                            ptx::tma_load_2d_pair_hint(sb + sub * L::kBBytes, &tma_b, leader_full, kx, n0, pol_b);
+                        }
                     }
                     if (++stage == STAGES) {
                         stage = 0;
@@ -163,7 +176,7 @@ gemm_bf16_sm100_2cta(const __grid_constant__ CUtensorMap tma_a, const __grid_con
                     break;
                 ptx::tcgen05_fence_after();
                 const uint32_t tmem_d = tmem_base + acc * BN;
-                for (uint32_t kb = 0; kb < num_kb; ++kb) {
+                for (uint32_t step = 0; step < num_steps; ++step) {
                     {
                         WaitTimer wt(prof);
                         ok = wait_bounded<true>(full_bar(stage), phase, ctl, 2);
@@ -173,13 +186,17 @@ gemm_bf16_sm100_2cta(const __grid_constant__ CUtensorMap tma_a, const __grid_con
                         break;
                     ptx::tcgen05_fence_after();
                     const uint32_t sa = smem_base + stage * L::kStageBytes;
-                    const uint64_t da = ptx::make_smem_desc_sw128(sa);
-                    const uint64_t db = ptx::make_smem_desc_sw128(sa + L::kABytes);
+                    const uint32_t sb = sa + KBS * L::kABytes;
 #pragma unroll
-                    for (uint32_t k = 0; k < kBlockK / kUmmaK; ++k)
-                        ptx::mma_bf16_2cta(tmem_d, da + 2u * k, db + 2u * k, kIdesc, (kb | k) != 0u ? 1u : 0u);
-                    ptx::mma_commit_2cta(empty_bar(stage));                      // leader's stage is free
-                    ptx::mma_commit_2cta(ptx::mapa_shared(empty_bar(stage), 1));  // and the peer's
+                    for (uint32_t sub = 0; sub < KBS; ++sub) {
+                        const uint64_t da = ptx::make_smem_desc_sw128(sa + sub * L::kABytes);
+                        const uint64_t db = ptx::make_smem_desc_sw128(sb + sub * L::kBBytes);
+#pragma unroll
+                        for (uint32_t k = 0; k < kBlockK / kUmmaK; ++k)
+                            ptx::mma_bf16_2cta(tmem_d, da + 2u * k, db + 2u * k, kIdesc,
+                                               (step | sub | k) != 0u ? 1u : 0u);
+                    }
+                    ptx::mma_commit_2cta_mask(empty_bar(stage), 3);  // stage s of both CTAs is free
                     if (++stage == STAGES) {
                         stage = 0;
                         phase ^= 1u;
@@ -187,8 +204,7 @@ gemm_bf16_sm100_2cta(const __grid_constant__ CUtensorMap tma_a, const __grid_con
                 }
                 if (!ok)
                     break;
-                ptx::mma_commit_2cta(acc_full_bar(acc));
-                ptx::mma_commit_2cta(ptx::mapa_shared(acc_full_bar(acc), 1));
+                ptx::mma_commit_2cta_mask(acc_full_bar(acc), 3);  // both halves of the accumulator are complete
                 if (++acc == 2) {
                     acc = 0;
                     acc_phase ^= 1u;

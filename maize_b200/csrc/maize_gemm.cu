@@ -41,17 +41,14 @@ const KernelVariant kVariants[] = {
     {"sm100_1cta_128x64x64_s8", 128, 64, 64, 1},
     {"sm100_1cta_128x32x64_s8", 128, 32, 32, 1},
     {"sm100_2cta_256x256x64_s6", 256, 256, 128, 2},
-    // skinny-M kernels: block_m = the MMA's N side (rows of A it can take), block_n = rows of B per tile
-    {"sm100_skinny_m16_128x64_s10", 16, 128, 128, 1},
-    {"sm100_skinny_m32_128x64_s9", 32, 128, 128, 1},
-    {"sm100_skinny_m64_128x64_s8", 64, 128, 128, 1},
-    {"sm100_skinny_m128_128x64_s6", 128, 128, 128, 1},
-    {"sm100_skinny_m16_128x128_s5", 16, 128, 128, 1},
-    {"sm100_skinny_m32_128x128_s5", 32, 128, 128, 1},
-    {"sm100_skinny_m64_128x128_s4", 64, 128, 128, 1},
+    {"sm100_2cta_256x256x128_s3", 256, 256, 128, 2},
+    // stream-K kernels for M <= 128: block_m = rows of A they take, block_n = rows of B per tile
+    {"sm100_skinny_m32_128x256x64_s4", 32, 256, 256, 1},
+    {"sm100_skinny_m128_128x256x64_s4", 128, 256, 256, 1},
 };
-constexpr int kFirstSkinny = 5;  // indices of the skinny variants
-constexpr int kLastSkinny = 11;
+constexpr int kPairWide = 5;     // index of the CTA-pair kernel with 128-wide stages
+constexpr int kFirstSkinny = 6;  // indices of the skinny variants
+constexpr int kLastSkinny = 7;
 constexpr int kNumVariants = static_cast<int>(sizeof(kVariants) / sizeof(kVariants[0]));
 constexpr int kMaxProfileCtas = 1024;
 constexpr size_t kPartialsBytes = size_t(32) << 20;  // stream-K scratch per context
@@ -87,6 +84,7 @@ struct maize_ctx {
     int force_kernel = 0;
     int max_ctas = 0;
     uint32_t debug_flags = 0;
+    uint32_t group_rows = 2048;
     uint64_t launches = 0;
     EncodeTiledFn encode = nullptr;
     void *staging = nullptr;  // device staging for the *_host entry point
@@ -169,19 +167,19 @@ int pick_variant(const maize_ctx_t *ctx, uint32_t m, uint32_t n, uint32_t k)
     const uint32_t sms = ctx ? static_cast<uint32_t>(ctx->sm_count) : 148u;
     const uint64_t tiles_m = (m + maize::kBlockM - 1) / maize::kBlockM;
     // One row-block of A or less: the shape is bound by streaming B, take the stream-K kernels.
-    if (m <= 16)
-        return kFirstSkinny;
     if (m <= 32)
-        return kFirstSkinny + 1;
-    if (m <= 64)
-        return kFirstSkinny + 2;
+        return kFirstSkinny;
     if (m <= 128 && (uint64_t(n) + 255) / 256 < 2ull * sms)
-        return kFirstSkinny + 3;
+        return kFirstSkinny + 1;
     // Widest tile whose tile count still fills the machine reasonably; narrow N gets narrow tiles.
     if (n <= 32)
         return 3;
     if (n <= 64)
         return 2;
+    // Enough 256 x 256 tiles for every CTA pair: the pair kernel moves a third less data per SM.
+    const uint64_t pair_tiles = ((uint64_t(m) + 255) / 256) * ((uint64_t(n) + 255) / 256);
+    if (m > 128 && n > 128 && pair_tiles >= sms / 2)
+        return kPairWide;
     const uint64_t tiles256 = tiles_m * ((n + 255) / 256);
     if (n > 128 && tiles256 >= 2ull * sms)
         return 0;
@@ -197,13 +195,12 @@ int pick_variant(const maize_ctx_t *ctx, uint32_t m, uint32_t n, uint32_t k)
     return 2;
 }
 
-template <uint32_t MMA_N, uint32_t KBS, uint32_t STAGES>
-maize_status_t launch_skinny(maize_ctx_t *ctx, int vi, const CUtensorMap &tw, const CUtensorMap &tx,
+template <bool REPL, uint32_t STAGES>
+maize_status_t launch_skinny(maize_ctx_t *ctx, int vi, const CUtensorMap &tx, const CUtensorMap &tw,
                              maize::SkinnyParams p, cudaStream_t stream)
 {
-    using L = maize::SkinnySmemLayout<MMA_N, KBS, STAGES>;
-    auto kernel = maize::gemm_bf16_sm100_skinny<MMA_N, KBS, STAGES>;
-    p.num_kb = (p.k + maize::kBlockK * KBS - 1) / (maize::kBlockK * KBS);
+    using L = maize::SkinnySmemLayout<STAGES>;
+    auto kernel = maize::gemm_bf16_sm100_skinny<REPL, STAGES>;
     if (!ctx->attr_set[vi]) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes);
         if (e != cudaSuccess)
@@ -217,8 +214,12 @@ maize_status_t launch_skinny(maize_ctx_t *ctx, int vi, const CUtensorMap &tw, co
         cap = static_cast<uint32_t>(ctx->max_ctas);
     const uint64_t units = uint64_t(p.tiles_n) * p.num_kb;
     uint64_t q = (units + cap - 1) / cap;
+    // every exchange of partials costs a few microseconds of latency: do not split below 8 k-blocks per CTA
+    const uint64_t min_q = p.num_kb < 8 ? p.num_kb : 8;
+    if (q < min_q)
+        q = min_q;
     auto parts_bound = [&](uint64_t per_cta) { return (p.num_kb - 1 + per_cta - 1) / per_cta + 1; };
-    const size_t slot_bytes = size_t(MMA_N) * 128 * sizeof(float);
+    const size_t slot_bytes = size_t(maize::kSkinnyTileN) * (REPL ? 32 : 128) * sizeof(float);
     const bool plenty = p.tiles_n >= 8ull * cap;
     if (plenty || p.tiles_n > kMaxSkinnyTiles || size_t(p.tiles_n) * parts_bound(q) * slot_bytes > kPartialsBytes)
         q = ((q + p.num_kb - 1) / p.num_kb) * p.num_kb;  // whole tiles: every tile has one part
@@ -227,7 +228,7 @@ maize_status_t launch_skinny(maize_ctx_t *ctx, int vi, const CUtensorMap &tw, co
     p.units_per_cta = static_cast<uint32_t>(q);
     p.max_parts = (q % p.num_kb == 0) ? 1u : static_cast<uint32_t>(parts_bound(q));
     const uint32_t grid = static_cast<uint32_t>((units + q - 1) / q);
-    kernel<<<grid, maize::kNumThreads, L::kDynamicBytes, stream>>>(tw, tx, p);
+    kernel<<<grid, maize::kNumThreads, L::kDynamicBytes, stream>>>(tx, tw, p);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess)
         return fail_cuda(ctx, "kernel launch", e);
@@ -272,36 +273,36 @@ maize_status_t gemm_impl(maize_ctx_t *ctx, const void *a, uint64_t lda, const vo
     if (vi >= kFirstSkinny && vi <= kLastSkinny) {
         if (m > kv.block_m)
             return fail(ctx, MAIZE_ERR_UNSUPPORTED, "forced skinny kernel takes fewer rows of A than M");
-        CUtensorMap tw, tx;
-        maize_status_t sst = make_operand_map(ctx, &tw, b, n, k, ldb, maize::kSkinnyTileN);
+        const bool repl = vi == kFirstSkinny;
+        CUtensorMap tx, tw;
+        maize_status_t sst = make_operand_map(ctx, &tx, a, m, k, lda, repl ? 32 : 128);
         if (sst != MAIZE_OK)
             return sst;
-        sst = make_operand_map(ctx, &tx, a, m, k, lda, kv.block_m);
+        sst = make_operand_map(ctx, &tw, b, n, k, ldb, maize::kSkinnyTileN);
         if (sst != MAIZE_OK)
             return sst;
         maize::SkinnyParams sp;
-        sp.c = static_cast<__nv_bfloat16 *>(c);
-        sp.ldc = ldc;
-        sp.m = m;
-        sp.n = n;
-        sp.k = k;
+        sp.g.c = static_cast<__nv_bfloat16 *>(c);
+        sp.g.ldc = ldc;
+        sp.g.m = m;
+        sp.g.n = n;
+        sp.g.k = k;
+        sp.g.tiles_m = 1;
+        sp.g.tiles_n = 0;
+        sp.g.group_m = 1;
+        sp.g.c_vec_ok = (ldc % 8 == 0 && reinterpret_cast<uintptr_t>(c) % 16 == 0) ? 1u : 0u;
+        sp.g.status = ctx->d_status;
+        sp.g.timeout_ns = ctx->timeout_ns;
+        sp.g.profile = nullptr;
+        sp.g.debug_flags = ctx->debug_flags;
         sp.tiles_n = (n + maize::kSkinnyTileN - 1) / maize::kSkinnyTileN;
         sp.num_kb = (k + maize::kBlockK - 1) / maize::kBlockK;
         sp.units_per_cta = 0;
         sp.max_parts = 1;
         sp.partials = ctx->d_partials;
         sp.counters = ctx->d_counters;
-        sp.status = ctx->d_status;
-        sp.timeout_ns = ctx->timeout_ns;
-        switch (vi - kFirstSkinny) {
-        case 0: return launch_skinny<16, 1, 10>(ctx, vi, tw, tx, sp, stream);
-        case 1: return launch_skinny<32, 1, 9>(ctx, vi, tw, tx, sp, stream);
-        case 2: return launch_skinny<64, 1, 8>(ctx, vi, tw, tx, sp, stream);
-        case 3: return launch_skinny<128, 1, 6>(ctx, vi, tw, tx, sp, stream);
-        case 4: return launch_skinny<16, 2, 5>(ctx, vi, tw, tx, sp, stream);
-        case 5: return launch_skinny<32, 2, 5>(ctx, vi, tw, tx, sp, stream);
-        default: return launch_skinny<64, 2, 4>(ctx, vi, tw, tx, sp, stream);
-        }
+        return repl ? launch_skinny<true, 4>(ctx, vi, tx, tw, sp, stream)
+                    : launch_skinny<false, 4>(ctx, vi, tx, tw, sp, stream);
     }
 
     CUtensorMap ta, tb;
@@ -320,7 +321,9 @@ maize_status_t gemm_impl(maize_ctx_t *ctx, const void *a, uint64_t lda, const vo
     p.k = k;
     p.tiles_m = (m + kv.block_m - 1) / kv.block_m;
     p.tiles_n = (n + kv.block_n - 1) / kv.block_n;
-    p.group_m = 2048 / kv.block_m;  // row-blocks swept together: 2048 rows of A stay hot in L2
+    p.group_m = ctx->group_rows / kv.block_m;  // row-blocks swept together: their rows of A stay hot in L2
+    if (p.group_m == 0)
+        p.group_m = 1;
     p.c_vec_ok = (ldc % 8 == 0 && reinterpret_cast<uintptr_t>(c) % 16 == 0) ? 1u : 0u;
     p.status = ctx->d_status;
     p.timeout_ns = ctx->timeout_ns;
@@ -346,9 +349,12 @@ maize_status_t gemm_impl(maize_ctx_t *ctx, const void *a, uint64_t lda, const vo
     case 1: return launch_variant<128, 6>(ctx, vi, ta, tb, p, grid, stream);
     case 2: return launch_variant<64, 8>(ctx, vi, ta, tb, p, grid, stream);
     case 3: return launch_variant<32, 8>(ctx, vi, ta, tb, p, grid, stream);
+    case 4:
+        return launch_kernel(ctx, vi, maize::gemm_bf16_sm100_2cta<256, 1, 6>,
+                             maize::PairSmemLayout<256, 1, 6>::kDynamicBytes, ta, tb, p, grid, stream);
     default:
-        return launch_kernel(ctx, vi, maize::gemm_bf16_sm100_2cta<256, 6>, maize::PairSmemLayout<256, 6>::kDynamicBytes,
-                             ta, tb, p, grid, stream);
+        return launch_kernel(ctx, vi, maize::gemm_bf16_sm100_2cta<256, 2, 3>,
+                             maize::PairSmemLayout<256, 2, 3>::kDynamicBytes, ta, tb, p, grid, stream);
     }
 }
 
@@ -570,6 +576,10 @@ maize_status_t maize_ctx_set(maize_ctx_t *ctx, const char *key, int64_t value)
             cudaFree(ctx->d_profile);
             ctx->d_profile = nullptr;
         }
+    } else if (!strcmp(key, "group_rows")) {
+        if (value < 128 || value > (1 << 24))
+            return fail(ctx, MAIZE_ERR_INVALID_ARG, "group_rows out of range");
+        ctx->group_rows = static_cast<uint32_t>(value);
     } else if (!strcmp(key, "debug_flags")) {
         ctx->debug_flags = static_cast<uint32_t>(value);
     } else if (!strcmp(key, "max_ctas")) {

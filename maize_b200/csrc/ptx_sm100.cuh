@@ -158,6 +158,16 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t smem_dst, const CUtens
         : "memory");
 }
 
+__device__ __forceinline__ void tma_load_2d_pair_hint(uint32_t smem_dst, const CUtensorMap *map,
+                                                      uint32_t bar_cluster_addr, int32_t x, int32_t y, uint64_t policy)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+        " [%0], [%1, {%3, %4}], [%2], %5;" ::"r"(smem_dst),
+        "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster_addr), "r"(x), "r"(y), "l"(policy)
+        : "memory");
+}
+
 // Arrive (release, cluster scope) on a barrier named by a shared::cluster address.
 __device__ __forceinline__ void mbar_arrive_cluster_addr(uint32_t bar_cluster_addr)
 {
@@ -180,6 +190,13 @@ __device__ __forceinline__ uint64_t policy_evict_last()
 {
     uint64_t p;
     asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+
+__device__ __forceinline__ uint64_t policy_evict_normal()
+{
+    uint64_t p;
+    asm volatile("createpolicy.fractional.L2::evict_normal.b64 %0, 1.0;" : "=l"(p));
     return p;
 }
 
@@ -325,6 +342,17 @@ __device__ __forceinline__ void mma_commit_2cta(uint32_t bar_cluster_addr)
 {
     asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
                      bar_cluster_addr)
+                 : "memory");
+}
+
+// CTA-pair commit that arrives on the barrier at the same offset in every CTA named by
+// `cta_mask` (bit i = CTA rank i of the cluster) with one instruction.  This is a barrier
+// signal, not a data copy.
+__device__ __forceinline__ void mma_commit_2cta_mask(uint32_t bar, uint16_t cta_mask)
+{
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
+                     bar),
+                 "h"(cta_mask)
                  : "memory");
 }
 
