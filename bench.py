@@ -45,7 +45,11 @@ def parse_args():
     p.add_argument("--warmup", type=int, default=5)
     p.add_argument("--workload", default="c4", choices=sorted(WORKLOADS))
     p.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    p.add_argument("--slabs", type=int, default=8, help="row slabs of A for the overlapped broadcast (N > 1)")
+    p.add_argument("--slabs", type=int, default=0,
+                   help="row slabs of A for the overlapped broadcast (N > 1); 0 = sizes from the makespan model")
+    p.add_argument("--transport", default="auto", choices=["auto", "multimem", "nccl"],
+                   help="how A reaches the other GPUs at N > 1 (auto: NVSwitch multicast push when available)")
+    p.add_argument("--push-ctas", type=int, default=0, help="CTAs of the multicast push kernel (0 = library default)")
     p.add_argument("--e2e-steps", type=int, default=3)
     p.add_argument("--no-cpu-baseline", action="store_true")
     p.add_argument("--force-kernel", type=int, default=0, help="kernel variant id (0 = the library's heuristic)")
@@ -193,6 +197,9 @@ def main():
     import maize_b200
     from maize_b200.sharded import NShardedGemm, shard_bounds
 
+    # NCCL prints its version banner on stdout at VERSION level; stdout must carry the JSON line only
+    if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
+        os.environ["NCCL_DEBUG"] = "WARN"
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -232,7 +239,8 @@ def main():
         sets.append((draw((m, k), sa, gen) if rank == 0 else None, draw((ns, k), sb, gen_b),
                      torch.empty((m, ns), dtype=torch.bfloat16, device=dev)))
     a_root, b_shard, c_shard = sets[0]
-    op = NShardedGemm(m, n, k, slabs=args.slabs, ctx=ctx, device=dev)
+    op = NShardedGemm(m, n, k, slabs=args.slabs, ctx=ctx, device=dev, transport=args.transport,
+                      push_ctas=args.push_ctas)
     step_no = [0]
 
     def step():
@@ -268,8 +276,12 @@ def main():
     t_wall1 = time.time()
     launches = ctx.launch_count - launches0
     ctx.poll()
+    per_rank_ms = [ms_total / args.steps]
     if world > 1:
         t = torch.tensor([ms_total], dtype=torch.float64, device=dev)
+        allt = [torch.zeros_like(t) for _ in range(world)]
+        dist.all_gather(allt, t)
+        per_rank_ms = [round(float(x.item()) / args.steps, 4) for x in allt]
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms_total = float(t.item())
         lt = torch.tensor([launches], dtype=torch.int64, device=dev)
@@ -377,10 +389,12 @@ def main():
             "config": {"workload": f"{args.workload}: {desc}", "M": m, "N": n, "K": k,
                        "layout": "A MxK row-major, B NxK K-major, C MxN bf16",
                        "parallelism": "single GPU" if world == 1 else
-                                      f"N-sharded x{world}, A broadcast from rank 0 over NCCL in {len(op.slabs)} row slabs",
+                                      f"N-sharded x{world}, A replicated from rank 0 in {len(op.slabs)} row slabs over "
+                                      + ("NVSwitch multicast (multimem.st push kernel)" if op.transport == "multimem"
+                                         else "NCCL broadcast"),
                        "l2": (f"rotating over {n_sets} independent input sets ({n_sets * rank_bytes >> 20} MiB > 4x L2), "
                               "back-to-back launches") if small else "inputs exceed L2 (back-to-back launches)",
-                       "algorithmic_bytes": total_bytes},
+                       "algorithmic_bytes": total_bytes, "ms_per_step_by_rank": per_rank_ms},
             "roofline": roof, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
         }
         print(json.dumps(line), flush=True)

@@ -159,6 +159,39 @@ MAIZE_API uint64_t maize_ctx_launch_count(const maize_ctx_t *ctx);
 MAIZE_API int maize_ctx_read_profile(maize_ctx_t *ctx, uint64_t *out, int max_ctas, void *cuda_stream);
 
 /*
+ * Building blocks of the N-sharded multi-GPU path (the reference has none; they serve the
+ * split of B's column panels, crates/maize_tile/src/gmem/col_panel.rs:88-124, across GPUs).
+ *
+ * maize_mc_push: copy `bytes` from local device memory `src` to EVERY GPU's replica of a
+ * symmetric buffer through its NVSwitch multicast address `mc_dst` (multimem.st), then publish
+ * `flag_value` in the 32-bit word at multicast address `mc_flag` on every GPU.  16-byte aligned
+ * pointers and size.  `ctas` = CTAs of the push kernel (0 = default 32).  One push at a time per
+ * context.
+ * maize_mc_push_after: the same, but the kernel first waits (bounded) until the local word
+ * `wait_flag` has reached `wait_value`: for a source that another GPU is still filling.
+ * maize_scatter_push (root): split `bytes` of `src` into `world` equal chunks (16-byte units) and
+ * store chunk p into `peer_dst[p]` + its offset (peer-mapped landing buffer of rank p, given at
+ * the slab's base), then publish `flag_value` in `peer_flag[p]`; the root's own chunk is skipped.
+ * `peer_dst` / `peer_flag` are host arrays of `world` device pointers.
+ * maize_flags_wait: enqueue a bounded device-side wait until each of `count` (<= 32) consecutive
+ * 32-bit words at `flags` (local memory, written by peers) has reached `value` (values only grow;
+ * wrap-around safe).  An expired wait is reported by maize_ctx_poll as MAIZE_ERR_TIMEOUT.
+ * maize_flag_store: enqueue a system-scope release store of `value` to `flag`, which may be a
+ * peer-mapped address, ordered after the stream's earlier work.
+ */
+MAIZE_API maize_status_t maize_mc_push(maize_ctx_t *ctx, const void *src, void *mc_dst, uint64_t bytes, void *mc_flag,
+                                       uint32_t flag_value, int ctas, void *cuda_stream);
+MAIZE_API maize_status_t maize_mc_push_after(maize_ctx_t *ctx, const void *wait_flag, uint32_t wait_value,
+                                             const void *src, void *mc_dst, uint64_t bytes, void *mc_flag,
+                                             uint32_t flag_value, int ctas, void *cuda_stream);
+MAIZE_API maize_status_t maize_scatter_push(maize_ctx_t *ctx, const void *src, void *const *peer_dst,
+                                            void *const *peer_flag, uint32_t world, uint32_t root, uint64_t bytes,
+                                            uint32_t flag_value, int ctas, void *cuda_stream);
+MAIZE_API maize_status_t maize_flags_wait(maize_ctx_t *ctx, const void *flags, uint32_t count, uint32_t value,
+                                          void *cuda_stream);
+MAIZE_API maize_status_t maize_flag_store(maize_ctx_t *ctx, void *flag, uint32_t value, void *cuda_stream);
+
+/*
  * Self-test of the bounded-wait machinery: launches one CTA that waits on a
  * barrier nothing will ever complete, with a budget of `budget_ns`.  The kernel
  * returns by itself; the following maize_ctx_poll reports MAIZE_ERR_TIMEOUT.

@@ -46,6 +46,11 @@ SYMBOLS = {
     "maize_ctx_launch_count": (_u64, [_vp]),
     "maize_debug_wait_expires": (_int, [_vp, _u64, _vp]),
     "maize_ctx_read_profile": (_int, [_vp, ctypes.POINTER(_u64), _int, _vp]),
+    "maize_mc_push": (_int, [_vp, _vp, _vp, _u64, _vp, _u32, _int, _vp]),
+    "maize_mc_push_after": (_int, [_vp, _vp, _u32, _vp, _vp, _u64, _vp, _u32, _int, _vp]),
+    "maize_scatter_push": (_int, [_vp, _vp, ctypes.POINTER(_vp), ctypes.POINTER(_vp), _u32, _u32, _u64, _u32, _int, _vp]),
+    "maize_flags_wait": (_int, [_vp, _vp, _u32, _u32, _vp]),
+    "maize_flag_store": (_int, [_vp, _vp, _u32, _vp]),
 }
 
 _lib = None

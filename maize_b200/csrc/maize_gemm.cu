@@ -16,6 +16,7 @@
 #include "gemm_sm100.cuh"
 #include "gemm_sm100_2cta.cuh"
 #include "gemm_sm100_skinny.cuh"
+#include "mc_bcast.cuh"
 
 namespace {
 
@@ -92,6 +93,7 @@ struct maize_ctx {
     bool attr_set[kNumVariants] = {};
     float *d_partials = nullptr;        // stream-K scratch of the skinny kernels
     unsigned int *d_counters = nullptr;  // arrival counters, zero between launches
+    unsigned int *d_push_counter = nullptr;  // [0]: CTA arrivals of the multicast push; [16 + p]: of the scatter per rank
     unsigned long long *d_profile = nullptr;  // kProfileSlots counters per CTA, allocated when "profile" is set
     int profile_ctas = 0;                      // CTAs of the last profiled launch
     std::string err;
@@ -418,6 +420,8 @@ maize_status_t maize_ctx_create(int device, maize_ctx_t **out)
     if (cudaMalloc(&ctx->d_status, sizeof(DeviceStatus)) != cudaSuccess ||
         cudaMemset(ctx->d_status, 0, sizeof(DeviceStatus)) != cudaSuccess ||
         cudaMalloc(&ctx->d_partials, kPartialsBytes) != cudaSuccess ||
+        cudaMalloc(&ctx->d_push_counter, sizeof(unsigned int) * 32) != cudaSuccess ||
+        cudaMemset(ctx->d_push_counter, 0, sizeof(unsigned int) * 32) != cudaSuccess ||
         cudaMalloc(&ctx->d_counters, sizeof(unsigned int) * 4 * kMaxSkinnyTiles) != cudaSuccess ||
         cudaMemset(ctx->d_counters, 0, sizeof(unsigned int) * 4 * kMaxSkinnyTiles) != cudaSuccess ||
         cudaMallocHost(&ctx->h_status, sizeof(DeviceStatus)) != cudaSuccess) {
@@ -445,6 +449,8 @@ void maize_ctx_destroy(maize_ctx_t *ctx)
         cudaFree(ctx->d_partials);
     if (ctx->d_counters)
         cudaFree(ctx->d_counters);
+    if (ctx->d_push_counter)
+        cudaFree(ctx->d_push_counter);
     delete ctx;
 }
 
@@ -636,6 +642,107 @@ int maize_ctx_read_profile(maize_ctx_t *ctx, uint64_t *out, int max_ctas, void *
     if (cudaMemcpy(out, ctx->d_profile, sizeof(uint64_t) * maize::kProfileSlots * n, cudaMemcpyDeviceToHost) != cudaSuccess)
         return 0;
     return n;
+}
+
+maize_status_t maize_mc_push_after(maize_ctx_t *ctx, const void *wait_flag, uint32_t wait_value, const void *src,
+                                   void *mc_dst, uint64_t bytes, void *mc_flag, uint32_t flag_value, int ctas,
+                                   void *cuda_stream)
+{
+    if (!ctx)
+        return MAIZE_ERR_INVALID_ARG;
+    if (!src || !mc_dst || !mc_flag)
+        return fail(ctx, MAIZE_ERR_INVALID_ARG, "null pointer");
+    if (bytes % 16 != 0 || reinterpret_cast<uintptr_t>(src) % 16 != 0 || reinterpret_cast<uintptr_t>(mc_dst) % 16 != 0 ||
+        reinterpret_cast<uintptr_t>(mc_flag) % 4 != 0 || reinterpret_cast<uintptr_t>(wait_flag) % 4 != 0)
+        return fail(ctx, MAIZE_ERR_UNSUPPORTED, "multicast push needs 16-byte aligned buffers and size");
+    if (ctas <= 0)
+        ctas = 32;
+    if (ctas > 4 * ctx->sm_count)
+        ctas = 4 * ctx->sm_count;
+    DeviceGuard guard(ctx->device);
+    maize::mc_push_kernel<<<ctas, 512, 0, static_cast<cudaStream_t>(cuda_stream)>>>(
+        static_cast<const uint4 *>(src), static_cast<uint4 *>(mc_dst), bytes / 16, ctx->d_push_counter,
+        static_cast<uint32_t *>(mc_flag), flag_value, static_cast<const uint32_t *>(wait_flag), wait_value,
+        ctx->d_status, ctx->timeout_ns);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess)
+        return fail_cuda(ctx, "kernel launch", e);
+    ctx->launches += 1;
+    return MAIZE_OK;
+}
+
+maize_status_t maize_mc_push(maize_ctx_t *ctx, const void *src, void *mc_dst, uint64_t bytes, void *mc_flag,
+                             uint32_t flag_value, int ctas, void *cuda_stream)
+{
+    return maize_mc_push_after(ctx, nullptr, 0, src, mc_dst, bytes, mc_flag, flag_value, ctas, cuda_stream);
+}
+
+maize_status_t maize_scatter_push(maize_ctx_t *ctx, const void *src, void *const *peer_dst, void *const *peer_flag,
+                                  uint32_t world, uint32_t root, uint64_t bytes, uint32_t flag_value, int ctas,
+                                  void *cuda_stream)
+{
+    if (!ctx)
+        return MAIZE_ERR_INVALID_ARG;
+    if (!src || !peer_dst || !peer_flag || world < 2 || world > maize::kMaxPeers || root >= world)
+        return fail(ctx, MAIZE_ERR_INVALID_ARG, "scatter: bad pointer, world size or root");
+    if (bytes % 16 != 0 || reinterpret_cast<uintptr_t>(src) % 16 != 0)
+        return fail(ctx, MAIZE_ERR_UNSUPPORTED, "scatter needs 16-byte aligned buffers and size");
+    maize::ScatterTargets t = {};
+    for (uint32_t p = 0; p < world; ++p) {
+        if (p == root)
+            continue;
+        if (!peer_dst[p] || !peer_flag[p] || reinterpret_cast<uintptr_t>(peer_dst[p]) % 16 != 0 ||
+            reinterpret_cast<uintptr_t>(peer_flag[p]) % 4 != 0)
+            return fail(ctx, MAIZE_ERR_INVALID_ARG, "scatter: bad peer pointer");
+        t.dst[p] = static_cast<uint4 *>(peer_dst[p]);
+        t.flag[p] = static_cast<uint32_t *>(peer_flag[p]);
+    }
+    const uint32_t peers = world - 1;
+    if (ctas <= 0)
+        ctas = 32;
+    uint32_t grid = static_cast<uint32_t>(ctas);
+    if (grid < peers)
+        grid = peers;  // at least one CTA per peer
+    grid = (grid + peers - 1) / peers * peers;
+    DeviceGuard guard(ctx->device);
+    maize::scatter_push_kernel<<<grid, 512, 0, static_cast<cudaStream_t>(cuda_stream)>>>(
+        static_cast<const uint4 *>(src), t, bytes / 16, world, root, flag_value, ctx->d_push_counter + 16);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess)
+        return fail_cuda(ctx, "kernel launch", e);
+    ctx->launches += 1;
+    return MAIZE_OK;
+}
+
+maize_status_t maize_flags_wait(maize_ctx_t *ctx, const void *flags, uint32_t count, uint32_t value, void *cuda_stream)
+{
+    if (!ctx)
+        return MAIZE_ERR_INVALID_ARG;
+    if (!flags || count == 0 || count > 32 || reinterpret_cast<uintptr_t>(flags) % 4 != 0)
+        return fail(ctx, MAIZE_ERR_INVALID_ARG, "flags: 1 to 32 aligned 32-bit words");
+    DeviceGuard guard(ctx->device);
+    maize::flags_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(cuda_stream)>>>(
+        static_cast<const uint32_t *>(flags), count, value, ctx->d_status, ctx->timeout_ns);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess)
+        return fail_cuda(ctx, "kernel launch", e);
+    ctx->launches += 1;
+    return MAIZE_OK;
+}
+
+maize_status_t maize_flag_store(maize_ctx_t *ctx, void *flag, uint32_t value, void *cuda_stream)
+{
+    if (!ctx)
+        return MAIZE_ERR_INVALID_ARG;
+    if (!flag || reinterpret_cast<uintptr_t>(flag) % 4 != 0)
+        return fail(ctx, MAIZE_ERR_INVALID_ARG, "flag: aligned 32-bit word");
+    DeviceGuard guard(ctx->device);
+    maize::flag_store_kernel<<<1, 32, 0, static_cast<cudaStream_t>(cuda_stream)>>>(static_cast<uint32_t *>(flag), value);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess)
+        return fail_cuda(ctx, "kernel launch", e);
+    ctx->launches += 1;
+    return MAIZE_OK;
 }
 
 maize_status_t maize_debug_wait_expires(maize_ctx_t *ctx, uint64_t budget_ns, void *cuda_stream)

@@ -156,6 +156,35 @@ class Context:
         n = self._lib.maize_ctx_read_profile(self._h, buf, 1024, _stream_handle(stream))
         return [dict(zip(self.PROFILE_SLOTS, buf[8 * i:8 * i + 8])) for i in range(n)]
 
+    # ------------------------------------------------- multi-GPU building blocks --
+    def mc_push(self, src_ptr: int, mc_dst_ptr: int, nbytes: int, mc_flag_ptr: int, flag_value: int, ctas: int = 0,
+                stream=None) -> None:
+        """Push local bytes to every GPU's replica through the multicast address, then publish a flag value."""
+        self._check(self._lib.maize_mc_push(self._h, src_ptr, mc_dst_ptr, nbytes, mc_flag_ptr, flag_value & 0xFFFFFFFF,
+                                            ctas, _stream_handle(stream)))
+
+    def mc_push_after(self, wait_flag_ptr: int, wait_value: int, src_ptr: int, mc_dst_ptr: int, nbytes: int,
+                      mc_flag_ptr: int, flag_value: int, ctas: int = 0, stream=None) -> None:
+        """Like mc_push, but the kernel first waits for the local word at wait_flag_ptr to reach wait_value."""
+        self._check(self._lib.maize_mc_push_after(self._h, wait_flag_ptr, wait_value & 0xFFFFFFFF, src_ptr, mc_dst_ptr,
+                                                  nbytes, mc_flag_ptr, flag_value & 0xFFFFFFFF, ctas,
+                                                  _stream_handle(stream)))
+
+    def scatter_push(self, src_ptr: int, peer_dst_ptrs, peer_flag_ptrs, root: int, nbytes: int, flag_value: int,
+                     ctas: int = 0, stream=None) -> None:
+        """Root: store chunk p of the source into rank p's landing buffer and publish a flag there."""
+        world = len(peer_dst_ptrs)
+        dst = (ctypes.c_void_p * world)(*[ctypes.c_void_p(int(x)) for x in peer_dst_ptrs])
+        flg = (ctypes.c_void_p * world)(*[ctypes.c_void_p(int(x)) for x in peer_flag_ptrs])
+        self._check(self._lib.maize_scatter_push(self._h, src_ptr, dst, flg, world, root, nbytes,
+                                                 flag_value & 0xFFFFFFFF, ctas, _stream_handle(stream)))
+
+    def flags_wait(self, flags_ptr: int, count: int, value: int, stream=None) -> None:
+        self._check(self._lib.maize_flags_wait(self._h, flags_ptr, count, value & 0xFFFFFFFF, _stream_handle(stream)))
+
+    def flag_store(self, flag_ptr: int, value: int, stream=None) -> None:
+        self._check(self._lib.maize_flag_store(self._h, flag_ptr, value & 0xFFFFFFFF, _stream_handle(stream)))
+
     def debug_wait_expires(self, budget_ns: int, stream=None) -> None:
         self._check(self._lib.maize_debug_wait_expires(self._h, int(budget_ns), _stream_handle(stream)))
 

@@ -7,10 +7,22 @@ rows ``[r*N/G, (r+1)*N/G)`` of B (N x K, K-major, so a contiguous block) and pro
 matching column block of C into its own dense M x (N/G) buffer.  Output columns are
 independent, so the only exchange is the replication of A: no reduction.
 
-A is cut into row slabs.  The broadcasts of all slabs are queued first (NCCL runs them in
-order on its own stream); the GEMM of slab i only waits for broadcast i, so the transfer of
-slab i+1 overlaps the math of slab i and only the first slab's transfer is exposed.  The
-broadcast lands in this GPU's own memory; kernels only ever read local memory.
+A is cut into row slabs; the GEMM of slab i only waits for slab i to land, so the transfer of
+slab i+1 overlaps the math of slab i.  Two transports:
+
+* ``multimem`` (GPUs with an NVSwitch multicast mapping, the default there), two stages per
+  slab: the root stores chunk p (1/G of the slab) into rank p's symmetric landing buffer with
+  unicast stores; every rank then pushes its own chunk to ALL ranks through the switch with
+  ``multimem.st`` and publishes a per-rank slab counter the same way.  One source alone tops
+  out near 400 GB/s of multicast; G sources in parallel use every GPU's links.  The copy
+  kernels are thin enough to share SMs with the persistent GEMM; each GEMM launch is preceded
+  by a one-warp bounded wait on the G counters.  Landing buffers are double-buffered across
+  steps; ranks acknowledge a finished step in the root's memory so that nothing overwrites a
+  buffer that is still being read.
+* ``nccl``: ``torch.distributed.broadcast`` per slab (any backend; used by the CPU/gloo tests).
+  Its wide CTAs cannot share an SM with the GEMM's, so on 8 GPUs transfer and math serialise.
+
+Either way the data lands in this GPU's own memory; GEMM kernels only ever read local memory.
 """
 from __future__ import annotations
 
@@ -43,6 +55,54 @@ def slab_bounds(m: int, slabs: int, align: int = 128) -> List[Tuple[int, int]]:
     return out
 
 
+def plan_slabs(m: int, shard_cols: int, k: int, *, tile_rows: int = 256, tile_cols: int = 256, in_flight: int = 74,
+               gemm_tflops: float = 1350.0, bcast_gbs: float = 600.0, per_slab_us: float = 25.0,
+               max_slabs: int = 16) -> List[Tuple[int, int]]:
+    """Row slabs of A that minimise the modelled time of one step on a non-root rank.
+
+    Model: the broadcast of a slab takes rows * K * 2 bytes / ``bcast_gbs`` and slabs are sent back to
+    back; the GEMM of a slab starts when its broadcast has landed and the previous GEMM is done, and takes
+    ceil(tiles / in_flight) waves of ``tile_rows x tile_cols`` tiles at ``gemm_tflops`` plus ``per_slab_us``
+    of launch overhead.  Because the bytes sent so far depend only on the rows sent so far, "earliest
+    finish of the first b row-blocks" is an exact dynamic programme over b.  The result keeps the first
+    slab small when the step is compute-bound, the last slab small when it is transfer-bound, and sizes
+    every slab to a whole number of tile waves.
+    """
+    if m <= 0:
+        return []
+    blocks = -(-m // tile_rows)
+    tiles_n = max(1, -(-shard_cols // tile_cols))
+    t_wave = in_flight * 2.0 * tile_rows * tile_cols * k / (gemm_tflops * 1e12)  # seconds per full wave
+    t_block = tile_rows * k * 2.0 / (bcast_gbs * 1e9)                            # seconds to send one row-block
+    overhead = per_slab_us * 1e-6
+    inf = float("inf")
+    # best[b][s] = earliest finish of the GEMMs of the first b blocks using s slabs
+    best = [[inf] * (max_slabs + 1) for _ in range(blocks + 1)]
+    prev = [[0] * (max_slabs + 1) for _ in range(blocks + 1)]
+    best[0][0] = 0.0
+    for b in range(blocks):
+        for s_used in range(max_slabs):
+            t_comp = best[b][s_used]
+            if t_comp == inf:
+                continue
+            for nxt in range(b + 1, blocks + 1):
+                landed = nxt * t_block
+                waves = -(-((nxt - b) * tiles_n) // in_flight)
+                done = max(t_comp, landed) + waves * t_wave + overhead
+                if done < best[nxt][s_used + 1]:
+                    best[nxt][s_used + 1] = done
+                    prev[nxt][s_used + 1] = b
+    s_best = min(range(1, max_slabs + 1), key=lambda s_: best[blocks][s_])
+    cuts = []
+    b, s_used = blocks, s_best
+    while b > 0:
+        pb = prev[b][s_used]
+        cuts.append((pb, b))
+        b, s_used = pb, s_used - 1
+    cuts.reverse()
+    return [(lo * tile_rows, min(m, hi * tile_rows)) for lo, hi in cuts]
+
+
 class NShardedGemm:
     """``C[:, shard] = A @ B[shard].T`` on every rank, A living on ``root`` before the call.
 
@@ -50,8 +110,9 @@ class NShardedGemm:
     CPU ranks (gloo) pass their own to exercise the partition and the exchange.
     """
 
-    def __init__(self, m: int, n: int, k: int, group=None, root: int = 0, slabs: int = 8,
-                 gemm_fn: Optional[Callable] = None, device=None, ctx=None):
+    def __init__(self, m: int, n: int, k: int, group=None, root: int = 0, slabs: int = 0,
+                 gemm_fn: Optional[Callable] = None, device=None, ctx=None, transport: str = "auto",
+                 push_ctas: int = 0, **plan_args):
         import torch
         import torch.distributed as dist
         self.dist = dist
@@ -61,14 +122,34 @@ class NShardedGemm:
         self.root = root
         self.m, self.n, self.k = m, n, k
         self.lo, self.hi = shard_bounds(n, self.world, self.rank)
-        self.slabs = slab_bounds(m, slabs if self.world > 1 else 1)
+        # slabs > 0: that many equal slabs; slabs == 0: sizes from the makespan model of plan_slabs()
+        if self.world == 1:
+            self.slabs = slab_bounds(m, 1)
+        elif slabs > 0:
+            self.slabs = slab_bounds(m, slabs)
+        else:
+            # every rank must cut A the same way: plan for the widest shard (rank 0's), not for its own
+            widest = shard_bounds(n, self.world, 0)
+            self.slabs = plan_slabs(m, widest[1] - widest[0], k, **plan_args)
         self.device = device
+        self.ctx = ctx
         if gemm_fn is None:
             from .gemm import default_context
             self.ctx = ctx or default_context(torch.device(device).index if device is not None else None)
             gemm_fn = lambda a, b, c: self.ctx.gemm(a, b, out=c)  # noqa: E731
         self.gemm_fn = gemm_fn
         self._a_local = None
+        self.push_ctas = push_ctas
+        self.step = 0
+        self.transport = "nccl"
+        self._mc = None
+        if self.world > 1 and transport in ("auto", "multimem") and getattr(self, "ctx", None) is not None:
+            try:
+                self._setup_multimem(device)
+                self.transport = "multimem"
+            except Exception:
+                if transport == "multimem":
+                    raise
 
     @property
     def shard_cols(self) -> int:
@@ -77,9 +158,102 @@ class NShardedGemm:
     def a_buffer(self, like):
         """This rank's landing buffer for A (the root uses its own A in place)."""
         import torch
+        if self._mc is not None:
+            return self._landing((self.step - 1) & 1 if self.step else 0)
         if self._a_local is None:
             self._a_local = torch.empty((self.m, self.k), dtype=like.dtype, device=like.device)
         return self._a_local
+
+    # ----------------------------------------------------------- multimem transport --
+    # 32-bit flag words behind the landing buffers of every rank:
+    #   [0, G)    word r counts the slabs whose chunk r has been multicast (written by rank r on every GPU)
+    #   [16]      slabs whose own chunk has landed here (written by the root with a unicast store)
+    #   [32, 32+G) on the root: word r = steps that rank r has finished reading (acknowledgements)
+    _FLAG_WORDS = 64
+    _W_LANDED, _W_ACK = 16, 32
+
+    def _setup_multimem(self, device):
+        import torch
+        import torch.distributed._symmetric_memory as symm_mem
+        if self.world > 16:
+            raise RuntimeError("multimem transport handles up to 16 GPUs")
+        group = self.group if self.group is not None else self.dist.group.WORLD
+        dev = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
+        slab_elems = self.m * self.k
+        self._buf_elems = -(-slab_elems // 128) * 128  # keep the second buffer 256-byte aligned
+        total = 2 * self._buf_elems + self._FLAG_WORDS * 2  # bf16 elements; flags are 32-bit = 2 elements each
+        buf = symm_mem.empty(total, dtype=torch.bfloat16, device=dev)
+        buf.zero_()
+        hdl = symm_mem.rendezvous(buf, group.group_name)
+        if not hdl.multicast_ptr:
+            raise RuntimeError("no multicast mapping for the symmetric buffer")
+        torch.cuda.synchronize(dev)
+        hdl.barrier()
+        self._mc = dict(
+            buf=buf, hdl=hdl, mc_base=int(hdl.multicast_ptr), local_base=buf.data_ptr(),
+            peer_base=[int(x) for x in hdl.buffer_ptrs], flags_off=2 * self._buf_elems * 2,
+            push_stream=torch.cuda.Stream(device=dev), dev=dev)
+
+    def _landing(self, parity: int):
+        """This rank's landing buffer of the given step parity, as an M x K tensor."""
+        mc = self._mc
+        return mc["buf"][parity * self._buf_elems: parity * self._buf_elems + self.m * self.k].view(self.m, self.k)
+
+    def _chunk(self, nbytes: int, rank: int) -> Tuple[int, int]:
+        """Byte range of rank's share of a slab of nbytes (equal shares in 16-byte units, as the kernels cut it)."""
+        n16 = nbytes // 16
+        return n16 * rank // self.world * 16, n16 * (rank + 1) // self.world * 16
+
+    def _run_multimem(self, a_root, b_shard, c_shard):
+        """Two-stage replication per slab: the root stores chunk p of the slab into rank p's landing buffer
+        (unicast), then every rank multicasts its own chunk to all ranks, so that all GPUs' links carry the
+        traffic instead of the root's alone.  A GEMM waits until all G chunks of its slab are in."""
+        import torch
+        mc, ctx, G = self._mc, self.ctx, self.world
+        n_slabs = len(self.slabs)
+        parity = self.step & 1
+        base = self.step * n_slabs
+        par_off = parity * self._buf_elems * 2
+        flags_mc = mc["mc_base"] + mc["flags_off"]
+        flags_local = mc["local_base"] + mc["flags_off"]
+        row_bytes = self.k * 2
+        cur = torch.cuda.current_stream(mc["dev"])
+        push = mc["push_stream"]
+        is_root = self.rank == self.root
+        if is_root:
+            push.wait_stream(cur)  # A may have been produced by earlier work of the caller's stream
+            if self.step >= 2:
+                # the buffer of this parity was last read in step - 2: every rank must have acknowledged it
+                ctx.flags_wait(flags_local + self._W_ACK * 4, G, self.step - 1, stream=push)
+        for i, (lo, hi) in enumerate(self.slabs):
+            nbytes = (hi - lo) * row_bytes
+            off = par_off + lo * row_bytes
+            c_lo, c_hi = self._chunk(nbytes, self.rank)
+            value = base + i + 1
+            if is_root:
+                ctx.scatter_push(a_root.data_ptr() + lo * row_bytes, [pb + off for pb in mc["peer_base"]],
+                                 [pb + mc["flags_off"] + self._W_LANDED * 4 for pb in mc["peer_base"]], self.root,
+                                 nbytes, value, ctas=self.push_ctas, stream=push)
+                if c_hi > c_lo:
+                    ctx.mc_push(a_root.data_ptr() + lo * row_bytes + c_lo, mc["mc_base"] + off + c_lo, c_hi - c_lo,
+                                flags_mc + self.rank * 4, value, ctas=self.push_ctas, stream=push)
+                else:
+                    ctx.flag_store(flags_mc + self.rank * 4, value, stream=push)
+            else:
+                ctx.mc_push_after(flags_local + self._W_LANDED * 4, value, mc["local_base"] + off + c_lo,
+                                  mc["mc_base"] + off + c_lo, max(c_hi - c_lo, 0), flags_mc + self.rank * 4, value,
+                                  ctas=self.push_ctas, stream=push)
+        a = a_root if is_root else self._landing(parity)
+        for i, (lo, hi) in enumerate(self.slabs):
+            if not is_root:
+                ctx.flags_wait(flags_local, G, base + i + 1, stream=cur)
+            self.gemm_fn(a[lo:hi], b_shard, c_shard[lo:hi])
+        if is_root:
+            cur.wait_stream(push)  # A must not change before the pushes have read it
+        ctx.flag_store(mc["peer_base"][self.root] + mc["flags_off"] + (self._W_ACK + self.rank) * 4, self.step + 1,
+                       stream=cur)
+        self.step += 1
+        return c_shard
 
     def run(self, a_root, b_shard, c_shard):
         """One step: replicate A from the root slab by slab and multiply as slabs arrive.
@@ -90,6 +264,8 @@ class NShardedGemm:
         if self.world == 1:
             self.gemm_fn(a_root, b_shard, c_shard)
             return c_shard
+        if self.transport == "multimem":
+            return self._run_multimem(a_root, b_shard, c_shard)
         is_root = self.rank == self.root
         a = a_root if is_root else self.a_buffer(b_shard)
         src = self.dist.get_global_rank(self.group, self.root) if self.group is not None else self.root

@@ -7,7 +7,7 @@ import socket
 import numpy as np
 import pytest
 
-from maize_b200.sharded import shard_bounds, slab_bounds
+from maize_b200.sharded import plan_slabs, shard_bounds, slab_bounds
 
 
 def test_shard_bounds_cover_and_balance():
@@ -31,6 +31,26 @@ def test_slab_bounds():
     assert all((hi - lo) % 128 == 0 for lo, hi in s[:-1]) and len(s) <= 8
     assert slab_bounds(16, 8) == [(0, 16)]
     assert slab_bounds(0, 4) == []
+
+
+def test_plan_slabs_covers_and_aligns():
+    for m, cols, k in [(16384, 2048, 16384), (16384, 8192, 16384), (8192, 3584, 8192), (8192, 14336, 8192),
+                       (4111, 1984, 4104), (100, 64, 64)]:
+        plan = plan_slabs(m, cols, k)
+        assert plan[0][0] == 0 and plan[-1][1] == m
+        assert all(a[1] == b[0] for a, b in zip(plan, plan[1:]))
+        assert all(lo % 256 == 0 for lo, _ in plan) and 1 <= len(plan) <= 16
+    # 8 GPUs on 16384^3: 8 column tiles per shard, 74 tile pairs in flight.  Every slab but the ones at
+    # the two ends should fill its waves almost completely.
+    plan = plan_slabs(16384, 2048, 16384)
+    fills = []
+    for lo, hi in plan:
+        tiles = (hi - lo) // 256 * 8
+        fills.append(tiles / (-(-tiles // 74) * 74))
+    assert sum(f * (hi - lo) for f, (lo, hi) in zip(fills, plan)) / 16384 > 0.9
+    # the model prefers several slabs when the transfer is comparable to the compute, one when it is free
+    assert len(plan) >= 3
+    assert len(plan_slabs(16384, 2048, 16384, bcast_gbs=1e9)) <= 2
 
 
 def _free_port():
