@@ -49,6 +49,8 @@ def parse_args():
                    help="row slabs of A for the overlapped broadcast (N > 1); 0 = sizes from the makespan model")
     p.add_argument("--transport", default="auto", choices=["auto", "multimem", "nccl"],
                    help="how A reaches the other GPUs at N > 1 (auto: NVSwitch multicast push when available)")
+    p.add_argument("--mc-stages", type=int, default=1, choices=[1, 2],
+                   help="multimem transport: 2 = root scatters chunks and every GPU multicasts its own, 1 = root multicasts all")
     p.add_argument("--push-ctas", type=int, default=0, help="CTAs of the multicast push kernel (0 = library default)")
     p.add_argument("--e2e-steps", type=int, default=3)
     p.add_argument("--no-cpu-baseline", action="store_true")
@@ -240,7 +242,7 @@ def main():
                      torch.empty((m, ns), dtype=torch.bfloat16, device=dev)))
     a_root, b_shard, c_shard = sets[0]
     op = NShardedGemm(m, n, k, slabs=args.slabs, ctx=ctx, device=dev, transport=args.transport,
-                      push_ctas=args.push_ctas)
+                      push_ctas=args.push_ctas, mc_stages=args.mc_stages)
     step_no = [0]
 
     def step():

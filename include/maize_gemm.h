@@ -135,7 +135,9 @@ MAIZE_API maize_status_t maize_ctx_poll(maize_ctx_t *ctx, void *cuda_stream);
 
 /* Tunables.  Keys: "timeout_ns" (device wait budget), "force_kernel" (0 = heuristic,
  * see maize_kernel_name), "max_ctas" (cap on the persistent grid, 0 = SM count),
- * "profile" (1 = per-CTA cycle accounting, see maize_ctx_read_profile), "debug_flags"
+ * "profile" (1 = per-CTA cycle accounting, see maize_ctx_read_profile), "group_rows" (rows of A
+ * whose tiles are scheduled together, default 2048), "push_threads" (threads per CTA of the copy
+ * kernels of the multi-GPU path, default 512), "debug_flags"
  * (performance diagnostics that make results WRONG: 1 = all loads hit one tile, 2 = no loads). */
 MAIZE_API maize_status_t maize_ctx_set(maize_ctx_t *ctx, const char *key, int64_t value);
 MAIZE_API maize_status_t maize_ctx_get(const maize_ctx_t *ctx, const char *key, int64_t *value);
@@ -165,7 +167,7 @@ MAIZE_API int maize_ctx_read_profile(maize_ctx_t *ctx, uint64_t *out, int max_ct
  * maize_mc_push: copy `bytes` from local device memory `src` to EVERY GPU's replica of a
  * symmetric buffer through its NVSwitch multicast address `mc_dst` (multimem.st), then publish
  * `flag_value` in the 32-bit word at multicast address `mc_flag` on every GPU.  16-byte aligned
- * pointers and size.  `ctas` = CTAs of the push kernel (0 = default 32).  One push at a time per
+ * pointers and size.  `ctas` = CTAs of the push kernel (0 = default 16).  One push at a time per
  * context.
  * maize_mc_push_after: the same, but the kernel first waits (bounded) until the local word
  * `wait_flag` has reached `wait_value`: for a source that another GPU is still filling.

@@ -10,15 +10,17 @@ independent, so the only exchange is the replication of A: no reduction.
 A is cut into row slabs; the GEMM of slab i only waits for slab i to land, so the transfer of
 slab i+1 overlaps the math of slab i.  Two transports:
 
-* ``multimem`` (GPUs with an NVSwitch multicast mapping, the default there), two stages per
-  slab: the root stores chunk p (1/G of the slab) into rank p's symmetric landing buffer with
-  unicast stores; every rank then pushes its own chunk to ALL ranks through the switch with
-  ``multimem.st`` and publishes a per-rank slab counter the same way.  One source alone tops
-  out near 400 GB/s of multicast; G sources in parallel use every GPU's links.  The copy
-  kernels are thin enough to share SMs with the persistent GEMM; each GEMM launch is preceded
-  by a one-warp bounded wait on the G counters.  Landing buffers are double-buffered across
-  steps; ranks acknowledge a finished step in the root's memory so that nothing overwrites a
-  buffer that is still being read.
+* ``multimem`` (GPUs with an NVSwitch multicast mapping, the default there): the root pushes each
+  slab ONCE through the switch with ``multimem.st`` into symmetric landing buffers on every GPU
+  and publishes a slab counter the same way (``mc_stages=1``, the default); receivers run no
+  copy kernel, only a one-warp bounded wait on the counter ahead of each GEMM launch.  With
+  ``mc_stages=2`` the root instead stores chunk p (1/G of the slab) into rank p's buffer with
+  unicast stores and every rank multicasts its own chunk, so that all GPUs' links carry the
+  traffic; on the 8-GPU boxes this was measured slower per step (2.0-2.3 ms against 1.73 ms on
+  16384^3) because every GPU's GEMM then shares its SMs with a copy kernel.  The copy kernels
+  use no shared memory and few registers, so their CTAs are co-resident with the persistent
+  GEMM's.  Landing buffers are double-buffered across steps; ranks acknowledge a finished step
+  in the root's memory so that nothing overwrites a buffer that is still being read.
 * ``nccl``: ``torch.distributed.broadcast`` per slab (any backend; used by the CPU/gloo tests).
   Its wide CTAs cannot share an SM with the GEMM's, so on 8 GPUs transfer and math serialise.
 
@@ -112,7 +114,7 @@ class NShardedGemm:
 
     def __init__(self, m: int, n: int, k: int, group=None, root: int = 0, slabs: int = 0,
                  gemm_fn: Optional[Callable] = None, device=None, ctx=None, transport: str = "auto",
-                 push_ctas: int = 0, **plan_args):
+                 push_ctas: int = 0, mc_stages: int = 1, **plan_args):
         import torch
         import torch.distributed as dist
         self.dist = dist
@@ -140,6 +142,7 @@ class NShardedGemm:
         self.gemm_fn = gemm_fn
         self._a_local = None
         self.push_ctas = push_ctas
+        self.mc_stages = mc_stages  # 2: root scatters chunks, every rank multicasts its own; 1: the root multicasts everything
         self.step = 0
         self.transport = "nccl"
         self._mc = None
@@ -230,6 +233,11 @@ class NShardedGemm:
             off = par_off + lo * row_bytes
             c_lo, c_hi = self._chunk(nbytes, self.rank)
             value = base + i + 1
+            if self.mc_stages == 1:
+                if is_root:
+                    ctx.mc_push(a_root.data_ptr() + lo * row_bytes, mc["mc_base"] + off, nbytes,
+                                flags_mc + self.rank * 4, value, ctas=self.push_ctas, stream=push)
+                continue
             if is_root:
                 ctx.scatter_push(a_root.data_ptr() + lo * row_bytes, [pb + off for pb in mc["peer_base"]],
                                  [pb + mc["flags_off"] + self._W_LANDED * 4 for pb in mc["peer_base"]], self.root,
@@ -245,7 +253,9 @@ class NShardedGemm:
                                   ctas=self.push_ctas, stream=push)
         a = a_root if is_root else self._landing(parity)
         for i, (lo, hi) in enumerate(self.slabs):
-            if not is_root:
+            if not is_root and self.mc_stages == 1:
+                ctx.flags_wait(flags_local + self.root * 4, 1, base + i + 1, stream=cur)
+            elif not is_root:
                 ctx.flags_wait(flags_local, G, base + i + 1, stream=cur)
             self.gemm_fn(a[lo:hi], b_shard, c_shard[lo:hi])
         if is_root:
