@@ -36,6 +36,13 @@ WORKLOADS = {
     "t": (8192, 8192, 8192, 1.0, 1.0, "normal", 5, "BF16 GEMM M=N=K=8192"),
 }
 L2_BYTES = 126 * 1024 * 1024
+# DRAM bytes per launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum of one ncu
+# capture on a B200; the summaries with the commands are under profiles/).  None where not captured.
+NCU_TRAFFIC = {
+    "c4": 9.39e9,   # profiles/gemm_pair_16384.md
+    "t": 1.214e9,   # profiles/gemm_pair_8192.md
+    "c3": 1.393e8,  # profiles/skinny_16x16384x4096.md
+}
 
 
 def parse_args():
@@ -54,6 +61,7 @@ def parse_args():
     p.add_argument("--push-ctas", type=int, default=0, help="CTAs of the multicast push kernel (0 = library default)")
     p.add_argument("--e2e-steps", type=int, default=3)
     p.add_argument("--no-cpu-baseline", action="store_true")
+    p.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (for profiler captures)")
     p.add_argument("--force-kernel", type=int, default=0, help="kernel variant id (0 = the library's heuristic)")
     p.add_argument("--cpu-seconds", type=float, default=10.0, help="target CPU time of the cpu_baseline sample")
     return p.parse_args()
@@ -314,6 +322,8 @@ def main():
     # ---- end to end through the host-buffer entry point (N = 1) or pinned copies + sharded step (N > 1)
     e2e = None
     try:
+        if args.no_e2e:
+            raise RuntimeError("skipped by --no-e2e")
         ha = torch.empty((m, k), dtype=torch.bfloat16).pin_memory() if rank == 0 else None
         hb = torch.empty((ns, k), dtype=torch.bfloat16).pin_memory()
         hc = torch.empty((m, ns), dtype=torch.bfloat16).pin_memory()
@@ -376,6 +386,7 @@ def main():
             roof = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                     "frac": achieved / peak, "traffic": None,
                     "peak_source": f"{peaks['source']} cuBLAS bf16 " + ("sustained" if long_run else "burst")}
+        roof["traffic"] = NCU_TRAFFIC.get(args.workload) if world == 1 else None
         roof["kernel"] = kernel_name
         roof["kernel_ms"] = kernel_ms
         cpu = None

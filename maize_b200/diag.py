@@ -1,0 +1,110 @@
+"""Performance diagnostics of the GEMM kernels, on cuda:0.
+
+    python -m maize_b200.diag roles  --shape 8192,8192,8192 --kernels 1,5,6 [--flags 0,1,2]
+    python -m maize_b200.diag sweep  --shape 16384,16384,16384 --kernel 6 --group-rows 2048,3072,4096 --flags 0,4,12
+    python -m maize_b200.diag launch --shape 16,256,64 [--kernel 7] [--flags 2] [--reps 3]
+
+``roles``  prints, per kernel variant and diagnostic flag, the time, the busiest CTA's cycle count, the
+           effective SM clock and the share of its life each role spent blocked (the library's own cycle
+           counters, ``maize_ctx_set("profile", 1)``).
+``sweep``  launches one GEMM per (group_rows, debug_flags) pair, for capture under ``ncu --metrics ...``.
+``launch`` launches one shape a few times, for ``ncu --metrics gpu__time_duration.sum``.
+
+Diagnostic flags (``maize_ctx_set("debug_flags", f)``; results are WRONG when set): 1 = every load fetches
+tile (0, 0) so all operand traffic hits in L2, 2 = no loads at all, 4 = A loaded with an evict-last L2 hint,
+8 = B loaded with evict-first (4 and 8: pair kernels only).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import statistics
+
+
+def _ints(text):
+    return [int(x) for x in text.split(",") if x != ""]
+
+
+def main():
+    import torch
+    import maize_b200
+
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("mode", choices=["roles", "sweep", "launch"])
+    ap.add_argument("--shape", default="8192,8192,8192", help="M,N,K")
+    ap.add_argument("--kernels", default="1,5,6")
+    ap.add_argument("--kernel", type=int, default=0)
+    ap.add_argument("--flags", default="0")
+    ap.add_argument("--group-rows", default="2048")
+    ap.add_argument("--reps", type=int, default=5)
+    args = ap.parse_args()
+
+    m, n, k = _ints(args.shape)
+    torch.cuda.set_device(0)
+    ctx = maize_b200.Context(0)
+    a = torch.randn(m, k, device="cuda").bfloat16()
+    b = torch.randn(n, k, device="cuda").bfloat16()
+    c = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
+
+    def timed(reps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            ctx.gemm(a, b, out=c)
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps
+
+    if args.mode == "roles":
+        for kern in _ints(args.kernels):
+            for flags in _ints(args.flags):
+                ctx.set("force_kernel", kern)
+                ctx.set("debug_flags", flags)
+                ctx.set("profile", 0)
+                timed(3)
+                ms = timed(args.reps)
+                ctx.set("profile", 1)
+                ms_prof = timed(1)
+                prof = ctx.read_profile()
+                ctx.set("profile", 0)
+                if not prof:
+                    print(json.dumps({"kernel": kern, "flags": flags, "ms": round(ms, 4), "note": "no role counters"}))
+                    continue
+                pair = "2cta" in ctx.pick_kernel(m, n, k)
+                lead = [p for i, p in enumerate(prof) if not pair or i % 2 == 0]
+                cyc = max(p["cta_cycles"] for p in prof)
+
+                def share(rows, key):
+                    return round(statistics.mean(p[key] / max(p["cta_cycles"], 1) for p in rows), 3)
+
+                print(json.dumps({
+                    "kernel": ctx.pick_kernel(m, n, k), "flags": flags, "ms": round(ms, 4),
+                    "tflops": round(2.0 * m * n * k / ms / 1e9, 1), "cta_cycles_max": cyc,
+                    "eff_sm_mhz": round(cyc / (ms_prof * 1e3)),
+                    "mma_wait_data": share(lead, "mma_wait_full"),
+                    "mma_wait_accumulator": share(lead, "mma_wait_acc_empty"),
+                    "producer_wait_stage": share(prof, "producer_wait_empty"),
+                    "epilogue_wait_accumulator": share(prof, "epilogue_wait_acc_full"),
+                    "epilogue_drain": share(prof, "epilogue_drain")}), flush=True)
+    elif args.mode == "sweep":
+        ctx.set("force_kernel", args.kernel)
+        for g in _ints(args.group_rows):
+            for flags in _ints(args.flags):
+                ctx.set("group_rows", g)
+                ctx.set("debug_flags", flags)
+                ms = timed(1)
+                print(json.dumps({"group_rows": g, "flags": flags, "ms": round(ms, 4)}), flush=True)
+    else:
+        ctx.set("force_kernel", args.kernel)
+        for flags in _ints(args.flags):
+            ctx.set("debug_flags", flags)
+            ms = timed(args.reps)
+            print(json.dumps({"kernel": ctx.pick_kernel(m, n, k), "flags": flags, "ms_per_launch": round(ms, 4)}),
+                  flush=True)
+    ctx.set("debug_flags", 0)
+    ctx.set("force_kernel", 0)
+    ctx.poll()
+
+
+if __name__ == "__main__":
+    main()
