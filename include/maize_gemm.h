@@ -200,6 +200,38 @@ MAIZE_API maize_status_t maize_flag_store(maize_ctx_t *ctx, void *flag, uint32_t
  */
 MAIZE_API maize_status_t maize_debug_wait_expires(maize_ctx_t *ctx, uint64_t budget_ns, void *cuda_stream);
 
+/*
+ * Allocation-free form of the skinny (M <= 32) GEMM.  It has no counterpart in the reference.
+ *
+ * For callers that must not allocate device memory where the GEMM is needed: services with a
+ * "no cudaMalloc after start-up" rule (everything reserved up front, so a late allocation can
+ * neither fail nor stall the device) and plugins whose host owns all device memory and hands out
+ * only the operand buffers.  It takes no context (creating one allocates).  The stream-K scratch of
+ * the kernel is a fixed array inside the library image: 8 MiB + 4.25 KiB on EVERY GPU that loads the
+ * library, held until the process exits.  It calls no cudaMalloc, cudaFree or allocating library
+ * routine.
+ *
+ * C = A * B^T as in maize_gemm_bf16, dense rows, on the CURRENT device (the one that owns a, b, c and
+ * the stream).  Limits: M <= 32; N <= 65536; the split of the work over the SMs must need at most
+ * 256 partial-sum slots (for example 16 x 16384 x 4096 needs exactly 256); K % 8 == 0, A and B
+ * 16-byte aligned.  Anything beyond is refused with MAIZE_ERR_UNSUPPORTED and a message in `errbuf`
+ * that states what was needed and what the scratch holds; use maize_gemm_bf16 with a context then.
+ *
+ * The FIRST call on each device looks up the array's device address, the SM count and the tensor-map
+ * encoder and sets the kernel's shared-memory limit; make that first call before any stream capture.
+ * Every call on a device uses the same array and finds what the previous call left there: the
+ * counters and the status word are cleared on `cuda_stream` before each launch.  Calls whose kernels
+ * could overlap on the GPU (different streams without a dependency) race on the array: order them.
+ *
+ * `device_status`: optional 16-byte device buffer (4-byte aligned, zero it yourself) that receives
+ * MAIZE_ERR_TIMEOUT in its first word if a bounded device wait expires; NULL = not reported.
+ * `errbuf` / `errbuf_len`: optional host buffer for the error text.
+ */
+MAIZE_API maize_status_t maize_gemm_bf16_skinny_static(const void *a, uint32_t a_rows, uint32_t a_cols, const void *b,
+                                                       uint32_t b_rows, uint32_t b_cols, void *c, uint32_t c_rows,
+                                                       uint32_t c_cols, void *cuda_stream, void *device_status,
+                                                       char *errbuf, size_t errbuf_len);
+
 #ifdef __cplusplus
 }
 #endif

@@ -7,6 +7,6 @@ computing needs the built library and a B200.
 """
 from . import tile  # noqa: F401
 from ._ffi import LIB_PATH, STATUS_NAMES  # noqa: F401
-from .gemm import Context, MaizeError, Matrix, default_context, gemm  # noqa: F401
+from .gemm import Context, MaizeError, Matrix, default_context, gemm, gemm_skinny_static  # noqa: F401
 
-__all__ = ["Context", "MaizeError", "Matrix", "default_context", "gemm", "tile", "LIB_PATH"]
+__all__ = ["Context", "MaizeError", "Matrix", "default_context", "gemm", "gemm_skinny_static", "tile", "LIB_PATH"]

@@ -45,6 +45,8 @@ SYMBOLS = {
     "maize_pick_kernel": (_int, [_vp, _u32, _u32, _u32]),
     "maize_ctx_launch_count": (_u64, [_vp]),
     "maize_debug_wait_expires": (_int, [_vp, _u64, _vp]),
+    "maize_gemm_bf16_skinny_static": (_int, [_vp, _u32, _u32, _vp, _u32, _u32, _vp, _u32, _u32, _vp, _vp,
+                                             ctypes.c_char_p, ctypes.c_size_t]),
     "maize_ctx_read_profile": (_int, [_vp, ctypes.POINTER(_u64), _int, _vp]),
     "maize_mc_push": (_int, [_vp, _vp, _vp, _u64, _vp, _u32, _int, _vp]),
     "maize_mc_push_after": (_int, [_vp, _vp, _u32, _vp, _vp, _u64, _vp, _u32, _int, _vp]),

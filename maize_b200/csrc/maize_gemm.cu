@@ -11,6 +11,7 @@
 
 #include <cstdio>
 #include <cstring>
+#include <mutex>
 #include <string>
 
 #include "gemm_sm100.cuh"
@@ -768,3 +769,214 @@ maize_status_t maize_debug_wait_expires(maize_ctx_t *ctx, uint64_t budget_ns, vo
 }
 
 }  // extern "C"
+
+// ------------------------------------------------------------------------------------------------
+// Allocation-free skinny GEMM.
+//
+// Some hosts may not call cudaMalloc at the point where they need a decode-shaped GEMM: a service with
+// a "no allocation after start-up" rule (everything is reserved up front so that a late allocation can
+// neither fail nor stall the device), or a plugin whose host owns every byte of device memory and hands
+// out only the operand buffers.  For them the stream-K scratch of the skinny kernel lives in the library
+// image itself, in the file-scope array below, instead of in a context (creating a context allocates).
+//
+// The array belongs to the module: every GPU that loads this library holds kStaticScratchBytes of it
+// until the process exits, whether or not the entry point is ever called.  In HOST code the array's
+// name is only a handle for the runtime, not a device address; the address a kernel may use comes from
+// cudaGetSymbolAddress, asked once per device with that device current (static_scratch_for_current_device).
+//
+// Every call on a device shares the one array, which keeps whatever the previous call left: the words
+// that must start at zero (arrival counters, status) are cleared on the caller's stream before each
+// launch; the partial-sum slots need no clearing because every slot is written before it is read.
+// Two calls whose kernels overlap on the GPU (different streams, no dependency) would use the same
+// slots and counters at once and corrupt each other: callers must order them.
+constexpr size_t kStaticSlots = 256;                          // partial-sum slots of 256 columns x 32 rows fp32
+constexpr size_t kStaticSlotBytes = size_t(256) * 32 * 4;     // 32 KiB
+constexpr size_t kStaticCounters = 1024;                      // 4 per 256-column tile: N <= 65536
+constexpr size_t kStaticHeaderBytes = 256 + kStaticCounters * sizeof(unsigned int);  // status word, counters
+constexpr size_t kStaticScratchBytes = kStaticHeaderBytes + kStaticSlots * kStaticSlotBytes;  // 8 MiB + 4.25 KiB
+
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+namespace {
+
+struct StaticDeviceState {
+    bool ready = false;
+    unsigned char *scratch = nullptr;  // device address of g_static_scratch on this device
+    int sm_count = 0;
+    EncodeTiledFn encode = nullptr;
+};
+constexpr int kMaxStaticDevices = 64;
+StaticDeviceState g_static_state[kMaxStaticDevices];
+std::mutex g_static_mutex;
+
+void put_error(char *errbuf, size_t errbuf_len, const std::string &msg)
+{
+    if (errbuf && errbuf_len > 0) {
+        const size_t n = msg.size() < errbuf_len - 1 ? msg.size() : errbuf_len - 1;
+        memcpy(errbuf, msg.data(), n);
+        errbuf[n] = '\0';
+    }
+}
+
+// One-time set-up for the CURRENT device: resolve the device address of the scratch array, the SM count,
+// the tensor-map encoder and the kernel's shared-memory limit.  Allocates nothing.
+maize_status_t static_scratch_for_current_device(StaticDeviceState **out, char *errbuf, size_t errbuf_len)
+{
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess || dev < 0) {
+        cudaGetLastError();
+        put_error(errbuf, errbuf_len, "no current CUDA device");
+        return MAIZE_ERR_NO_DEVICE;
+    }
+    if (dev >= kMaxStaticDevices) {
+        put_error(errbuf, errbuf_len, "device ordinal beyond the table of the allocation-free entry point");
+        return MAIZE_ERR_UNSUPPORTED;
+    }
+    std::lock_guard<std::mutex> lock(g_static_mutex);
+    StaticDeviceState &st = g_static_state[dev];
+    if (!st.ready) {
+        cudaDeviceProp prop;
+        if ((e = cudaGetDeviceProperties(&prop, dev)) != cudaSuccess) {
+            put_error(errbuf, errbuf_len, std::string("cudaGetDeviceProperties: ") + cudaGetErrorString(e));
+            return MAIZE_ERR_CUDA;
+        }
+        if (prop.major != 10) {
+            put_error(errbuf, errbuf_len, "the kernels are built for sm_100a only");
+            return MAIZE_ERR_UNSUPPORTED;
+        }
+        void *addr = nullptr;
+        // The symbol's name is a host-side stand-in; this asks the runtime where the array lives on THIS device.
+        if ((e = cudaGetSymbolAddress(&addr, g_static_scratch)) != cudaSuccess || !addr) {
+            put_error(errbuf, errbuf_len, std::string("cudaGetSymbolAddress(scratch): ") + cudaGetErrorString(e));
+            return MAIZE_ERR_CUDA;
+        }
+        void *fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+        if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess || !fn) {
+            put_error(errbuf, errbuf_len, "cuTensorMapEncodeTiled is not available from this driver");
+            return MAIZE_ERR_CUDA;
+        }
+        e = cudaFuncSetAttribute(maize::gemm_bf16_sm100_skinny<true, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 maize::SkinnySmemLayout<4>::kDynamicBytes);
+        if (e != cudaSuccess) {
+            put_error(errbuf, errbuf_len, std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(e));
+            return MAIZE_ERR_CUDA;
+        }
+        st.scratch = static_cast<unsigned char *>(addr);
+        st.sm_count = prop.multiProcessorCount;
+        st.encode = reinterpret_cast<EncodeTiledFn>(fn);
+        st.ready = true;
+    }
+    *out = &st;
+    return MAIZE_OK;
+}
+
+bool encode_static_map(const StaticDeviceState &st, CUtensorMap *map, const void *base, uint64_t rows, uint64_t cols,
+                       uint32_t box_rows)
+{
+    cuuint64_t gdim[2] = {cols, rows};
+    cuuint64_t gstride[1] = {cols * 2};
+    cuuint32_t box[2] = {maize::kBlockK, box_rows};
+    cuuint32_t estride[2] = {1, 1};
+    return st.encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(base), gdim, gstride, box, estride,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace
+
+extern "C" maize_status_t maize_gemm_bf16_skinny_static(const void *a, uint32_t a_rows, uint32_t a_cols, const void *b,
+                                                        uint32_t b_rows, uint32_t b_cols, void *c, uint32_t c_rows,
+                                                        uint32_t c_cols, void *cuda_stream, void *device_status,
+                                                        char *errbuf, size_t errbuf_len)
+{
+    put_error(errbuf, errbuf_len, "");
+    if (a_cols != b_cols || c_rows != a_rows || c_cols != b_rows) {
+        put_error(errbuf, errbuf_len, "shapes do not agree: A is M x K, B is N x K, C is M x N");
+        return MAIZE_ERR_INVALID_ARG;
+    }
+    const uint32_t m = a_rows, n = b_rows, k = a_cols;
+    if (m == 0 || n == 0)
+        return MAIZE_OK;
+    if (!a || !b || !c || k == 0) {
+        put_error(errbuf, errbuf_len, "null pointer or K == 0");
+        return MAIZE_ERR_INVALID_ARG;
+    }
+    if (m > 32) {
+        put_error(errbuf, errbuf_len, "the allocation-free entry point takes at most 32 rows of A (M <= 32)");
+        return MAIZE_ERR_UNSUPPORTED;
+    }
+    if (k % 8 != 0 || reinterpret_cast<uintptr_t>(a) % 16 != 0 || reinterpret_cast<uintptr_t>(b) % 16 != 0 ||
+        reinterpret_cast<uintptr_t>(c) % 2 != 0 || reinterpret_cast<uintptr_t>(device_status) % 4 != 0) {
+        put_error(errbuf, errbuf_len, "K must be a multiple of 8, A and B 16-byte aligned, C 2-byte aligned");
+        return MAIZE_ERR_UNSUPPORTED;
+    }
+    StaticDeviceState *st = nullptr;
+    maize_status_t rc = static_scratch_for_current_device(&st, errbuf, errbuf_len);
+    if (rc != MAIZE_OK)
+        return rc;
+
+    maize::SkinnyParams sp;
+    sp.tiles_n = (n + maize::kSkinnyTileN - 1) / maize::kSkinnyTileN;
+    sp.num_kb = (k + maize::kBlockK - 1) / maize::kBlockK;
+    const uint64_t units = uint64_t(sp.tiles_n) * sp.num_kb;
+    const uint64_t cap = static_cast<uint64_t>(st->sm_count);
+    uint64_t q = (units + cap - 1) / cap;
+    const uint64_t min_q = sp.num_kb < 8 ? sp.num_kb : 8;
+    if (q < min_q)
+        q = min_q;
+    const uint64_t parts = (q % sp.num_kb == 0) ? 1 : (sp.num_kb - 1 + q - 1) / q + 1;
+    const uint64_t slots = parts == 1 ? 0 : uint64_t(sp.tiles_n) * parts;
+    if (slots > kStaticSlots || uint64_t(sp.tiles_n) * 4 > kStaticCounters || q > 0xffffffffull) {
+        char msg[200];
+        snprintf(msg, sizeof msg,
+                 "problem needs %llu partial-sum slots and %llu counters; the static scratch holds %llu and %llu "
+                 "(use maize_gemm_bf16 with a context for larger N x K)",
+                 (unsigned long long)slots, (unsigned long long)(uint64_t(sp.tiles_n) * 4),
+                 (unsigned long long)kStaticSlots, (unsigned long long)kStaticCounters);
+        put_error(errbuf, errbuf_len, msg);
+        return MAIZE_ERR_UNSUPPORTED;
+    }
+    CUtensorMap tx, tw;
+    if (!encode_static_map(*st, &tx, a, m, k, 32) || !encode_static_map(*st, &tw, b, n, k, maize::kSkinnyTileN)) {
+        put_error(errbuf, errbuf_len, "cuTensorMapEncodeTiled rejected the operands");
+        return MAIZE_ERR_CUDA;
+    }
+    cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+    // Counters (and the library's own status word) must start at zero; the previous call, or one that gave
+    // up on a wait, may have left them otherwise.  A memset on the caller's stream allocates nothing.
+    cudaError_t e = cudaMemsetAsync(st->scratch, 0, kStaticHeaderBytes, stream);
+    if (e != cudaSuccess) {
+        put_error(errbuf, errbuf_len, std::string("cudaMemsetAsync: ") + cudaGetErrorString(e));
+        return MAIZE_ERR_CUDA;
+    }
+    sp.g.c = static_cast<__nv_bfloat16 *>(c);
+    sp.g.ldc = n;
+    sp.g.m = m;
+    sp.g.n = n;
+    sp.g.k = k;
+    sp.g.tiles_m = 1;
+    sp.g.tiles_n = 0;
+    sp.g.group_m = 1;
+    sp.g.c_vec_ok = (n % 8 == 0 && reinterpret_cast<uintptr_t>(c) % 16 == 0) ? 1u : 0u;
+    sp.g.status = device_status ? static_cast<DeviceStatus *>(device_status)
+                                : reinterpret_cast<DeviceStatus *>(st->scratch);
+    sp.g.timeout_ns = 2000000000ull;
+    sp.g.profile = nullptr;
+    sp.g.debug_flags = 0;
+    sp.units_per_cta = static_cast<uint32_t>(q);
+    sp.max_parts = static_cast<uint32_t>(parts);
+    sp.counters = reinterpret_cast<unsigned int *>(st->scratch + 256);
+    sp.partials = reinterpret_cast<float *>(st->scratch + kStaticHeaderBytes);
+    const uint32_t grid = static_cast<uint32_t>((units + q - 1) / q);
+    maize::gemm_bf16_sm100_skinny<true, 4>
+        <<<grid, maize::kNumThreads, maize::SkinnySmemLayout<4>::kDynamicBytes, stream>>>(tx, tw, sp);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        put_error(errbuf, errbuf_len, std::string("kernel launch: ") + cudaGetErrorString(e));
+        return MAIZE_ERR_CUDA;
+    }
+    return MAIZE_OK;
+}

@@ -205,3 +205,25 @@ def default_context(device: Optional[int] = None) -> Context:
 def gemm(a, b, out=None, stream=None):
     """``a @ b.T`` on the B200 kernels (module-level convenience over a cached Context)."""
     return default_context(a.device.index).gemm(a, b, out=out, stream=stream)
+
+
+def gemm_skinny_static(a, b, out, stream=None, device_status=None):
+    """``out = a @ b.T`` for M <= 32 through the entry point that allocates nothing.
+
+    For callers that may not allocate device memory at this point (so ``out`` must be passed in): the
+    kernel's scratch is a fixed array inside the library (8 MiB per GPU).  Shapes beyond what that array
+    can serve raise ``MaizeError(UNSUPPORTED)`` with the sizes in the message.  Calls that could overlap
+    on the GPU share the array and must be ordered by the caller.  ``device_status``: optional int32[4]
+    CUDA tensor that receives a timeout code.
+    """
+    lib = _ffi.load()
+    err = ctypes.create_string_buffer(256)
+    m, k = a.shape
+    n, kb = b.shape
+    st = lib.maize_gemm_bf16_skinny_static(a.data_ptr(), m, k, b.data_ptr(), n, kb, out.data_ptr(), out.shape[0],
+                                           out.shape[1], _stream_handle(stream),
+                                           device_status.data_ptr() if device_status is not None else None,
+                                           err, len(err))
+    if st != _ffi.OK:
+        raise MaizeError(st, err.value.decode())
+    return out
