@@ -118,8 +118,11 @@ MAIZE_API maize_status_t maize_gemm_bf16_ld(maize_ctx_t *ctx, const void *a, uin
 
 /*
  * End-to-end form with HOST buffers (pinned or pageable): copies A and B to the
- * device, runs the GEMM, copies C back, all on `cuda_stream`, and waits for the
- * result.  Device staging is cached in the context and grows on demand.
+ * device, runs the GEMM, copies C back, ordered after the earlier work of
+ * `cuda_stream`, and waits for the result.  Large problems are pipelined: B first,
+ * then A in row slabs whose GEMMs and C read-backs overlap the following uploads
+ * (two helper streams of the context).  Device staging is cached in the context and
+ * grows on demand.
  * Stands where a host caller of the traced kernel (src/main.rs:31-90) would.
  */
 MAIZE_API maize_status_t maize_gemm_bf16_host(maize_ctx_t *ctx, const void *a_host, uint32_t a_rows, uint32_t a_cols,

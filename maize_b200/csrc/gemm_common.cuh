@@ -169,6 +169,7 @@ __device__ __forceinline__ void store_chunk(const GemmParams &p, uint8_t *stage_
     const bool col_ok = col0 + lane < p.n;
     __nv_bfloat16 *dst = p.c + static_cast<uint64_t>(row0) * p.ldc + col0 + lane;
     const uint8_t *src = stage_warp + lane * 2;
+#pragma unroll 8
     for (uint32_t r = 0; r < rows; ++r) {
         const __nv_bfloat16 v = *reinterpret_cast<const __nv_bfloat16 *>(src + r * kStageRowBytes);
         if (col_ok)

@@ -53,6 +53,7 @@ constexpr int kFirstSkinny = 6;  // indices of the skinny variants
 constexpr int kLastSkinny = 7;
 constexpr int kNumVariants = static_cast<int>(sizeof(kVariants) / sizeof(kVariants[0]));
 constexpr int kMaxProfileCtas = 1024;
+constexpr int kMaxHostSlabs = 16;  // row slabs of A / C that the host entry point pipelines over PCIe
 constexpr size_t kPartialsBytes = size_t(32) << 20;  // stream-K scratch per context
 constexpr uint32_t kMaxSkinnyTiles = 65536;          // 4 counters each; N up to 8M rows
 
@@ -92,6 +93,10 @@ struct maize_ctx {
     EncodeTiledFn encode = nullptr;
     void *staging = nullptr;  // device staging for the *_host entry point
     size_t staging_bytes = 0;
+    // helper streams and events of the *_host entry point (created on first use)
+    cudaStream_t copy_in = nullptr, copy_out = nullptr;
+    cudaEvent_t ev_start = nullptr, ev_done = nullptr;
+    cudaEvent_t ev_in[kMaxHostSlabs] = {}, ev_gemm[kMaxHostSlabs] = {};
     bool attr_set[kNumVariants] = {};
     float *d_partials = nullptr;        // stream-K scratch of the skinny kernels
     unsigned int *d_counters = nullptr;  // arrival counters, zero between launches
@@ -445,6 +450,20 @@ void maize_ctx_destroy(maize_ctx_t *ctx)
         cudaFreeHost(ctx->h_status);
     if (ctx->staging)
         cudaFree(ctx->staging);
+    if (ctx->copy_in)
+        cudaStreamDestroy(ctx->copy_in);
+    if (ctx->copy_out)
+        cudaStreamDestroy(ctx->copy_out);
+    if (ctx->ev_start)
+        cudaEventDestroy(ctx->ev_start);
+    if (ctx->ev_done)
+        cudaEventDestroy(ctx->ev_done);
+    for (int i = 0; i < kMaxHostSlabs; ++i) {
+        if (ctx->ev_in[i])
+            cudaEventDestroy(ctx->ev_in[i]);
+        if (ctx->ev_gemm[i])
+            cudaEventDestroy(ctx->ev_gemm[i]);
+    }
     if (ctx->d_profile)
         cudaFree(ctx->d_profile);
     if (ctx->d_partials)
@@ -524,17 +543,73 @@ maize_status_t maize_gemm_bf16_host(maize_ctx_t *ctx, const void *a_host, uint32
     char *db = da + round_up(a_bytes);
     char *dc = db + round_up(b_bytes);
     cudaError_t e;
-    if (a_bytes && (e = cudaMemcpyAsync(da, a_host, a_bytes, cudaMemcpyHostToDevice, stream)) != cudaSuccess)
-        return fail_cuda(ctx, "H2D copy of A", e);
-    if (b_bytes && (e = cudaMemcpyAsync(db, b_host, b_bytes, cudaMemcpyHostToDevice, stream)) != cudaSuccess)
+    // Small problems: one copy in, one GEMM, one copy out, all on the caller's stream.
+    // Large ones: B goes first, then A in row slabs on a copy stream; the GEMM of slab i starts when slab i
+    // has landed and the rows of C it produces go back on a second copy stream, so that the H2D of slab
+    // i+1, the math of slab i and the D2H of slab i-1 overlap (PCIe is full duplex; the GPU has several
+    // copy engines).  The call still returns only when C is complete in host memory.
+    const uint32_t m = a_rows, n = b_rows, k = a_cols;
+    uint32_t nslabs = 1;
+    if (a_bytes + b_bytes + c_bytes >= (size_t(64) << 20) && m >= 1024 && k > 0) {
+        nslabs = m / 1024;
+        if (nslabs > static_cast<uint32_t>(kMaxHostSlabs))
+            nslabs = kMaxHostSlabs;
+    }
+    if (nslabs <= 1) {
+        if (a_bytes && (e = cudaMemcpyAsync(da, a_host, a_bytes, cudaMemcpyHostToDevice, stream)) != cudaSuccess)
+            return fail_cuda(ctx, "H2D copy of A", e);
+        if (b_bytes && (e = cudaMemcpyAsync(db, b_host, b_bytes, cudaMemcpyHostToDevice, stream)) != cudaSuccess)
+            return fail_cuda(ctx, "H2D copy of B", e);
+        maize_status_t st = gemm_impl(ctx, da, k, db, k, dc, n, m, n, k, stream);
+        if (st != MAIZE_OK)
+            return st;
+        if ((e = cudaMemcpyAsync(c_host, dc, c_bytes, cudaMemcpyDeviceToHost, stream)) != cudaSuccess)
+            return fail_cuda(ctx, "D2H copy of C", e);
+        if ((e = cudaStreamSynchronize(stream)) != cudaSuccess)
+            return fail_cuda(ctx, "cudaStreamSynchronize", e);
+        return MAIZE_OK;
+    }
+    if (!ctx->copy_in) {
+        bool ok = cudaStreamCreateWithFlags(&ctx->copy_in, cudaStreamNonBlocking) == cudaSuccess &&
+                  cudaStreamCreateWithFlags(&ctx->copy_out, cudaStreamNonBlocking) == cudaSuccess &&
+                  cudaEventCreateWithFlags(&ctx->ev_start, cudaEventDisableTiming) == cudaSuccess &&
+                  cudaEventCreateWithFlags(&ctx->ev_done, cudaEventDisableTiming) == cudaSuccess;
+        for (int i = 0; ok && i < kMaxHostSlabs; ++i)
+            ok = cudaEventCreateWithFlags(&ctx->ev_in[i], cudaEventDisableTiming) == cudaSuccess &&
+                 cudaEventCreateWithFlags(&ctx->ev_gemm[i], cudaEventDisableTiming) == cudaSuccess;
+        if (!ok)
+            return fail_cuda(ctx, "creating the copy streams / events", cudaGetLastError());
+    }
+    const uint32_t slab_rows = ((m + nslabs - 1) / nslabs + 255) / 256 * 256;
+    // the copies must come after whatever the caller queued before this call
+    if ((e = cudaEventRecord(ctx->ev_start, stream)) != cudaSuccess ||
+        (e = cudaStreamWaitEvent(ctx->copy_in, ctx->ev_start, 0)) != cudaSuccess ||
+        (e = cudaStreamWaitEvent(ctx->copy_out, ctx->ev_start, 0)) != cudaSuccess)
+        return fail_cuda(ctx, "ordering the copy streams", e);
+    if ((e = cudaMemcpyAsync(db, b_host, b_bytes, cudaMemcpyHostToDevice, ctx->copy_in)) != cudaSuccess)
         return fail_cuda(ctx, "H2D copy of B", e);
-    maize_status_t st = gemm_impl(ctx, da, a_cols, db, b_cols, dc, c_cols, a_rows, b_rows, a_cols, stream);
-    if (st != MAIZE_OK)
-        return st;
-    if ((e = cudaMemcpyAsync(c_host, dc, c_bytes, cudaMemcpyDeviceToHost, stream)) != cudaSuccess)
-        return fail_cuda(ctx, "D2H copy of C", e);
-    if ((e = cudaStreamSynchronize(stream)) != cudaSuccess)
-        return fail_cuda(ctx, "cudaStreamSynchronize", e);
+    uint32_t used = 0;
+    for (uint32_t row0 = 0; row0 < m; row0 += slab_rows, ++used) {
+        const uint32_t rows = (m - row0 < slab_rows) ? (m - row0) : slab_rows;
+        const size_t a_off = size_t(row0) * k * 2, c_off = size_t(row0) * n * 2;
+        if ((e = cudaMemcpyAsync(da + a_off, static_cast<const char *>(a_host) + a_off, size_t(rows) * k * 2,
+                                 cudaMemcpyHostToDevice, ctx->copy_in)) != cudaSuccess ||
+            (e = cudaEventRecord(ctx->ev_in[used], ctx->copy_in)) != cudaSuccess ||
+            (e = cudaStreamWaitEvent(stream, ctx->ev_in[used], 0)) != cudaSuccess)
+            return fail_cuda(ctx, "H2D copy of an A slab", e);
+        maize_status_t st = gemm_impl(ctx, da + a_off, k, db, k, dc + c_off, n, rows, n, k, stream);
+        if (st != MAIZE_OK)
+            return st;
+        if ((e = cudaEventRecord(ctx->ev_gemm[used], stream)) != cudaSuccess ||
+            (e = cudaStreamWaitEvent(ctx->copy_out, ctx->ev_gemm[used], 0)) != cudaSuccess ||
+            (e = cudaMemcpyAsync(static_cast<char *>(c_host) + c_off, dc + c_off, size_t(rows) * n * 2,
+                                 cudaMemcpyDeviceToHost, ctx->copy_out)) != cudaSuccess)
+            return fail_cuda(ctx, "D2H copy of a C slab", e);
+    }
+    if ((e = cudaEventRecord(ctx->ev_done, ctx->copy_out)) != cudaSuccess ||
+        (e = cudaStreamWaitEvent(stream, ctx->ev_done, 0)) != cudaSuccess ||
+        (e = cudaStreamSynchronize(stream)) != cudaSuccess)
+        return fail_cuda(ctx, "waiting for C", e);
     return MAIZE_OK;
 }
 

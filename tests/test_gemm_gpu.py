@@ -205,6 +205,23 @@ def test_host_entry_point(ctx, oracle):
     assert np.array_equal(pc.numpy().view(np.uint16), c)
 
 
+def test_host_entry_point_pipelined(ctx, oracle):
+    """Large enough for the slab pipeline (B first, A in row slabs, C rows read back as they finish), ragged M."""
+    import torch
+    m, n, k = 5000, 3000, 2048
+    a, b = make_inputs(oracle, m, n, k, 26)
+    ref = oracle.gemm_bf16(a, b)
+    pa = torch.from_numpy(a.view(np.int16)).pin_memory()
+    pb = torch.from_numpy(b.view(np.int16)).pin_memory()
+    pc = torch.zeros((m, n), dtype=torch.int16).pin_memory()
+    for _ in range(2):  # twice: staging and events are reused
+        pc.zero_()
+        ctx.gemm_host(pa.data_ptr(), m, k, pb.data_ptr(), n, k, pc.data_ptr(), m, n)
+        ctx.poll()
+        assert_parity(oracle, pc.numpy().view(np.uint16), ref, k, oracle.max_abs_bf16(a), oracle.max_abs_bf16(b),
+                      "pipelined host entry")
+
+
 @pytest.mark.parametrize("force", [0, 1, 6])
 @pytest.mark.parametrize("name", ["c1", "c2", "c3"])
 def test_baseline_configs_full(ctx, oracle, name, force):
