@@ -17,6 +17,7 @@
 #include "gemm_sm100.cuh"
 #include "gemm_sm100_2cta.cuh"
 #include "gemm_sm100_skinny.cuh"
+#include "gemm_sm100_skinny_pair.cuh"
 #include "mc_bcast.cuh"
 
 namespace {
@@ -47,10 +48,13 @@ const KernelVariant kVariants[] = {
     // stream-K kernels for M <= 128: block_m = rows of A they take, block_n = rows of B per tile
     {"sm100_skinny_m32_128x256x64_s4", 32, 256, 256, 1},
     {"sm100_skinny_m128_128x256x64_s4", 128, 256, 256, 1},
+    // K split over a CTA pair, halves added through distributed shared memory; tile width chosen per shape
+    {"sm100_skinny_pair_m32_128xNx64_s4", 32, 256, 256, 2},
 };
 constexpr int kPairWide = 5;     // index of the CTA-pair kernel with 128-wide stages
 constexpr int kFirstSkinny = 6;  // indices of the skinny variants
 constexpr int kLastSkinny = 7;
+constexpr int kSkinnyPair = 8;
 constexpr int kNumVariants = static_cast<int>(sizeof(kVariants) / sizeof(kVariants[0]));
 constexpr int kMaxProfileCtas = 1024;
 constexpr int kMaxHostSlabs = 16;  // row slabs of A / C that the host entry point pipelines over PCIe
@@ -168,16 +172,42 @@ maize_status_t launch_variant(maize_ctx_t *ctx, int variant_index, const CUtenso
                          maize::GemmSmemLayout<BN, STAGES>::kDynamicBytes, ta, tb, p, grid, stream);
 }
 
+// Tile width for the pair-split skinny kernel: the narrowest multiple of 32 for which one pair per tile
+// covers N in a single wave.  Returns 0 when that needs more than 256 columns per tile.  The estimates
+// (microseconds) compare it with the stream-K kernel: bytes of B per CTA at the per-SM share of the HBM
+// rate, plus the measured fixed costs (launch and set-up ~5 us; exchange of halves through shared memory
+// ~1.5 us against ~4 us through global memory).
+uint32_t skinny_pair_tile(uint32_t sms, uint32_t n, uint32_t k, double *est_pair_us, double *est_streamk_us)
+{
+    const uint32_t pairs = sms / 2;
+    if (pairs == 0)
+        return 0;
+    uint32_t bn = ((n + pairs - 1) / pairs + 31) / 32 * 32;
+    if (bn < 32)
+        bn = 32;
+    if (bn > 256)
+        return 0;
+    const double num_kb = (k + maize::kBlockK - 1) / maize::kBlockK;
+    const double bytes_per_us_per_sm = 6.3e6 / sms;  // 6.3 TB/s while streaming, shared by all SMs
+    const double kb_bytes = 128.0;                   // bytes of one row of B in one k-block
+    *est_pair_us = bn * ((num_kb + 1) / 2) * kb_bytes / bytes_per_us_per_sm + 6.5;
+    *est_streamk_us = double(n) * num_kb * kb_bytes / sms / bytes_per_us_per_sm + 9.0;
+    return bn;
+}
+
 int pick_variant(const maize_ctx_t *ctx, uint32_t m, uint32_t n, uint32_t k)
 {
-    (void)k;
     if (ctx && ctx->force_kernel >= 1 && ctx->force_kernel <= kNumVariants)
         return ctx->force_kernel - 1;
     const uint32_t sms = ctx ? static_cast<uint32_t>(ctx->sm_count) : 148u;
     const uint64_t tiles_m = (m + maize::kBlockM - 1) / maize::kBlockM;
     // One row-block of A or less: the shape is bound by streaming B, take the stream-K kernels.
-    if (m <= 32)
+    if (m <= 32) {
+        double pair_us = 0, streamk_us = 0;
+        if (skinny_pair_tile(sms, n, k, &pair_us, &streamk_us) != 0 && pair_us <= streamk_us)
+            return kSkinnyPair;
         return kFirstSkinny;
+    }
     if (m <= 128 && (uint64_t(n) + 255) / 256 < 2ull * sms)
         return kFirstSkinny + 1;
     // Widest tile whose tile count still fills the machine reasonably; narrow N gets narrow tiles.
@@ -279,6 +309,52 @@ maize_status_t gemm_impl(maize_ctx_t *ctx, const void *a, uint64_t lda, const vo
     const int vi = pick_variant(ctx, m, n, k);
     const KernelVariant &kv = kVariants[vi];
 
+    if (vi == kSkinnyPair) {
+        if (m > kv.block_m)
+            return fail(ctx, MAIZE_ERR_UNSUPPORTED, "forced skinny kernel takes fewer rows of A than M");
+        double pair_us = 0, streamk_us = 0;
+        const uint32_t bn = skinny_pair_tile(static_cast<uint32_t>(ctx->sm_count), n, k, &pair_us, &streamk_us);
+        if (bn == 0)
+            return fail(ctx, MAIZE_ERR_UNSUPPORTED, "forced pair-split skinny kernel: N needs more than one wave of tiles");
+        CUtensorMap tx, tw;
+        maize_status_t sst = make_operand_map(ctx, &tx, a, m, k, lda, 32);
+        if (sst != MAIZE_OK)
+            return sst;
+        sst = make_operand_map(ctx, &tw, b, n, k, ldb, bn);
+        if (sst != MAIZE_OK)
+            return sst;
+        maize::SkinnyPairParams pp;
+        pp.g.c = static_cast<__nv_bfloat16 *>(c);
+        pp.g.ldc = ldc;
+        pp.g.m = m;
+        pp.g.n = n;
+        pp.g.k = k;
+        pp.g.tiles_m = 1;
+        pp.g.tiles_n = 0;
+        pp.g.group_m = 1;
+        pp.g.c_vec_ok = (ldc % 8 == 0 && reinterpret_cast<uintptr_t>(c) % 16 == 0) ? 1u : 0u;
+        pp.g.status = ctx->d_status;
+        pp.g.timeout_ns = ctx->timeout_ns;
+        pp.g.profile = nullptr;
+        pp.g.debug_flags = 0;
+        pp.bn = bn;
+        pp.tiles_n = (n + bn - 1) / bn;
+        pp.num_kb = (k + maize::kBlockK - 1) / maize::kBlockK;
+        auto kernel = maize::gemm_bf16_sm100_skinny_pair<4>;
+        if (!ctx->attr_set[vi]) {
+            cudaError_t ea = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                  maize::SkinnySmemLayout<4>::kDynamicBytes);
+            if (ea != cudaSuccess)
+                return fail_cuda(ctx, "cudaFuncSetAttribute(max dynamic smem)", ea);
+            ctx->attr_set[vi] = true;
+        }
+        kernel<<<2 * pp.tiles_n, maize::kNumThreads, maize::SkinnySmemLayout<4>::kDynamicBytes, stream>>>(tx, tw, pp);
+        cudaError_t el = cudaGetLastError();
+        if (el != cudaSuccess)
+            return fail_cuda(ctx, "kernel launch", el);
+        ctx->launches += 1;
+        return MAIZE_OK;
+    }
     if (vi >= kFirstSkinny && vi <= kLastSkinny) {
         if (m > kv.block_m)
             return fail(ctx, MAIZE_ERR_UNSUPPORTED, "forced skinny kernel takes fewer rows of A than M");

@@ -81,6 +81,31 @@ def test_skinny_variants_forced(ctx, oracle, force, m):
     run_case(ctx, oracle, m, 1001, 136, seed=25, force=force)  # odd N: 2-byte aligned C rows
 
 
+@pytest.mark.parametrize("m,n,k", [
+    (16, 16384, 4096), (1, 9472, 64), (32, 4096, 4096), (7, 1000, 520), (16, 18944, 1088), (20, 33, 72),
+    (16, 8191, 136), (32, 16385, 264),
+])
+def test_skinny_pair_split(ctx, oracle, m, n, k):
+    """K split over a CTA pair with the halves added through shared memory: odd and single k-block counts,
+    every tile width from 32 to 256, ragged last tiles, unaligned C rows."""
+    run_case(ctx, oracle, m, n, k, seed=27, force=9)
+    run_case(ctx, oracle, m, n, k, seed=28, force=9)
+
+
+def test_skinny_pair_rejects_more_than_one_wave(ctx):
+    import torch
+    import maize_b200
+    a = torch.zeros((16, 64), dtype=torch.bfloat16, device="cuda")
+    b = torch.zeros((74 * 256 + 1, 64), dtype=torch.bfloat16, device="cuda")
+    ctx.set("force_kernel", 9)
+    try:
+        with pytest.raises(maize_b200.MaizeError) as e:
+            ctx.gemm(a, b)
+        assert e.value.status == maize_b200._ffi.UNSUPPORTED
+    finally:
+        ctx.set("force_kernel", 0)
+
+
 def test_skinny_is_deterministic(ctx, oracle):
     import torch
     a, b = make_inputs(oracle, 16, 16384, 4096, 23)
