@@ -60,6 +60,8 @@ def parse_args():
                    help="multimem transport: 2 = root scatters chunks and every GPU multicasts its own, 1 = root multicasts all")
     p.add_argument("--push-ctas", type=int, default=0, help="CTAs of the multicast push kernel (0 = library default)")
     p.add_argument("--e2e-steps", type=int, default=3)
+    p.add_argument("--b-layout", default="nk", choices=["nk", "kn"],
+                   help="nk: B stored N x K (the bench's contract); kn: B stored K x N as the reference demo walks it (N = 1 GPU only)")
     p.add_argument("--no-cpu-baseline", action="store_true")
     p.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (for profiler captures)")
     p.add_argument("--force-kernel", type=int, default=0, help="kernel variant id (0 = the library's heuristic)")
@@ -244,13 +246,17 @@ def main():
     # independent input sets that the bytes touched between two uses of a set exceed 4x L2.
     small = rank_bytes < 2 * L2_BYTES
     n_sets = max(1, -(-4 * L2_BYTES // rank_bytes)) if small else 1
+    kn = args.b_layout == "kn"
+    if kn and world != 1:
+        raise SystemExit("--b-layout kn is a single-GPU measurement")
     sets = []
     for _ in range(n_sets):
-        sets.append((draw((m, k), sa, gen) if rank == 0 else None, draw((ns, k), sb, gen_b),
+        sets.append((draw((m, k), sa, gen) if rank == 0 else None, draw((k, ns) if kn else (ns, k), sb, gen_b),
                      torch.empty((m, ns), dtype=torch.bfloat16, device=dev)))
     a_root, b_shard, c_shard = sets[0]
+    gemm_call = (lambda a_, b_, c_: ctx.gemm_kn(a_, b_, out=c_)) if kn else (lambda a_, b_, c_: ctx.gemm(a_, b_, out=c_))
     op = NShardedGemm(m, n, k, slabs=args.slabs, ctx=ctx, device=dev, transport=args.transport,
-                      push_ctas=args.push_ctas, mc_stages=args.mc_stages)
+                      push_ctas=args.push_ctas, mc_stages=args.mc_stages, gemm_fn=gemm_call if kn else None)
     step_no = [0]
 
     def step():
@@ -313,7 +319,7 @@ def main():
     for i in range(reps):
         _, b_i, c_i = sets[i % n_sets]
         a_i = sets[i % n_sets][0] if rank == 0 else a_res
-        ctx.gemm(a_i, b_i, out=c_i)
+        gemm_call(a_i, b_i, c_i)
     e1.record()
     torch.cuda.synchronize()
     kernel_ms = e0.elapsed_time(e1) / reps
@@ -324,6 +330,8 @@ def main():
     try:
         if args.no_e2e:
             raise RuntimeError("skipped by --no-e2e")
+        if kn:
+            raise RuntimeError("the host-buffer entry point takes B as N x K only")
         ha = torch.empty((m, k), dtype=torch.bfloat16).pin_memory() if rank == 0 else None
         hb = torch.empty((ns, k), dtype=torch.bfloat16).pin_memory()
         hc = torch.empty((m, ns), dtype=torch.bfloat16).pin_memory()
@@ -400,7 +408,8 @@ def main():
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "bf16 in, fp32 accumulate", "data": "synthetic",
             "config": {"workload": f"{args.workload}: {desc}", "M": m, "N": n, "K": k,
-                       "layout": "A MxK row-major, B NxK K-major, C MxN bf16",
+                       "layout": "A MxK row-major, B KxN row-major, C MxN bf16" if kn else
+                                 "A MxK row-major, B NxK K-major, C MxN bf16",
                        "parallelism": "single GPU" if world == 1 else
                                       f"N-sharded x{world}, A replicated from rank 0 in {len(op.slabs)} row slabs over "
                                       + ("NVSwitch multicast (multimem.st push kernel)" if op.transport == "multimem"

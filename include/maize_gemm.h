@@ -117,6 +117,21 @@ MAIZE_API maize_status_t maize_gemm_bf16_ld(maize_ctx_t *ctx, const void *a, uin
                                             void *cuda_stream);
 
 /*
+ * C = A * B with B stored K x N row-major (N contiguous): the layout the reference's demo walks,
+ * 16-column panels of a row-major matrix stepping 16 rows per k-step
+ * (crates/maize_tile/src/gmem/col_panel.rs:88-124, gmem_tile.rs:416-432, src/main.rs:57).
+ * a_cols == b_rows (= K), c is a_rows x b_cols.  Requires b_cols (ldb) % 8 == 0 and a_cols (lda) % 8 == 0,
+ * 16-byte aligned A and B; K itself may be any value.  B's tiles are loaded as 64-column boxes and fed
+ * to the tensor core as an MN-major operand; nothing is transposed in memory.
+ */
+MAIZE_API maize_status_t maize_gemm_bf16_kn(maize_ctx_t *ctx, const void *a, uint32_t a_rows, uint32_t a_cols,
+                                            const void *b, uint32_t b_rows, uint32_t b_cols, void *c, uint32_t c_rows,
+                                            uint32_t c_cols, void *cuda_stream);
+MAIZE_API maize_status_t maize_gemm_bf16_kn_ld(maize_ctx_t *ctx, const void *a, uint64_t lda, const void *b,
+                                               uint64_t ldb, void *c, uint64_t ldc, uint32_t m, uint32_t n,
+                                               uint32_t k, void *cuda_stream);
+
+/*
  * End-to-end form with HOST buffers (pinned or pageable): copies A and B to the
  * device, runs the GEMM, copies C back, ordered after the earlier work of
  * `cuda_stream`, and waits for the result.  Large problems are pipelined: B first,

@@ -37,6 +37,8 @@ SYMBOLS = {
     "maize_gemm_bf16": (_int, [_vp, _vp, _u32, _u32, _vp, _u32, _u32, _vp, _u32, _u32, _vp]),
     "maize_gemm_bf16_m": (_int, [_vp, _gm, _gm, _gm, _vp]),
     "maize_gemm_bf16_ld": (_int, [_vp, _vp, _u64, _vp, _u64, _vp, _u64, _u32, _u32, _u32, _vp]),
+    "maize_gemm_bf16_kn": (_int, [_vp, _vp, _u32, _u32, _vp, _u32, _u32, _vp, _u32, _u32, _vp]),
+    "maize_gemm_bf16_kn_ld": (_int, [_vp, _vp, _u64, _vp, _u64, _vp, _u64, _u32, _u32, _u32, _vp]),
     "maize_gemm_bf16_host": (_int, [_vp, _vp, _u32, _u32, _vp, _u32, _u32, _vp, _u32, _u32, _vp]),
     "maize_ctx_poll": (_int, [_vp, _vp]),
     "maize_ctx_set": (_int, [_vp, ctypes.c_char_p, _i64]),

@@ -51,7 +51,9 @@ struct GemmSmemLayout {
     static_assert(kDynamicBytes > 116224, "two CTAs could share an SM and contend for TMEM");
 };
 
-template <uint32_t BN, uint32_t STAGES>
+// B_KN: B is given K x N row-major (N contiguous) instead of N x K; its tiles are then loaded as BN / 64
+// boxes of {64 columns, 64 k-rows} and read by the MMA as an MN-major operand.
+template <uint32_t BN, uint32_t STAGES, bool B_KN = false>
 __global__ void __launch_bounds__(kNumThreads, 1)
 gemm_bf16_sm100_1cta(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                      const GemmParams p)
@@ -60,7 +62,9 @@ gemm_bf16_sm100_1cta(const __grid_constant__ CUtensorMap tma_a, const __grid_con
     static_assert(BN % 32 == 0 && BN >= 32 && BN <= 256, "UMMA N for M = 128 must be a multiple of 16 up to 256");
     constexpr uint32_t kTmemCols = 2 * BN;  // two accumulator buffers; 64..512, a power of two
     static_assert((kTmemCols & (kTmemCols - 1)) == 0 && kTmemCols >= 32 && kTmemCols <= 512, "bad TMEM size");
-    constexpr uint32_t kIdesc = ptx::make_instr_desc_bf16(kBlockM, BN);
+    constexpr uint32_t kIdesc = ptx::make_instr_desc_bf16(kBlockM, BN, B_KN);
+    constexpr uint32_t kChunkBytes = kBlockK * 128;  // one 64-column chunk of a K x N tile: 64 k-rows x 128 B
+    static_assert(!B_KN || BN % 64 == 0, "K x N tiles are loaded in chunks of 64 columns");
 
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -130,7 +134,14 @@ gemm_bf16_sm100_1cta(const __grid_constant__ CUtensorMap tma_a, const __grid_con
                     } else {
                         ptx::mbar_arrive_expect_tx(full_bar(stage), L::kStageBytes);
                         ptx::tma_load_2d(sa, &tma_a, full_bar(stage), static_cast<int32_t>(kb * kBlockK), m0);
-                        ptx::tma_load_2d(sb, &tma_b, full_bar(stage), static_cast<int32_t>(kb * kBlockK), n0);
+                        if constexpr (B_KN) {
+#pragma unroll
+                            for (uint32_t j = 0; j < BN / 64; ++j)  // x = column, y = k row
+                                ptx::tma_load_2d(sb + j * kChunkBytes, &tma_b, full_bar(stage),
+                                                 n0 + static_cast<int32_t>(64u * j), static_cast<int32_t>(kb * kBlockK));
+                        } else {
+                            ptx::tma_load_2d(sb, &tma_b, full_bar(stage), static_cast<int32_t>(kb * kBlockK), n0);
+                        }
                     }
                     if (++stage == STAGES) {
                         stage = 0;
@@ -170,12 +181,14 @@ gemm_bf16_sm100_1cta(const __grid_constant__ CUtensorMap tma_a, const __grid_con
                     ptx::tcgen05_fence_after();
                     const uint32_t sa = smem_base + stage * L::kStageBytes;
                     const uint64_t da = ptx::make_smem_desc_sw128(sa);
-                    const uint64_t db = ptx::make_smem_desc_sw128(sa + L::kABytes);
+                    const uint64_t db = B_KN ? ptx::make_smem_desc_sw128_mn(sa + L::kABytes, kChunkBytes)
+                                             : ptx::make_smem_desc_sw128(sa + L::kABytes);
+                    // per 16-element K step: +32 bytes in a K-major tile (+2 in the address >> 4 field),
+                    // +2048 bytes (two groups of 8 k-rows) in a K x N tile (+128)
+                    constexpr uint32_t kStepB = B_KN ? 128u : 2u;
 #pragma unroll
-                    for (uint32_t k = 0; k < kBlockK / kUmmaK; ++k) {
-                        // +32 bytes per 16-element K step: +2 in the (address >> 4) field
-                        ptx::mma_bf16_1cta(tmem_d, da + 2u * k, db + 2u * k, kIdesc, (kb | k) != 0u ? 1u : 0u);
-                    }
+                    for (uint32_t k = 0; k < kBlockK / kUmmaK; ++k)
+                        ptx::mma_bf16_1cta(tmem_d, da + 2u * k, db + kStepB * k, kIdesc, (kb | k) != 0u ? 1u : 0u);
                     ptx::mma_commit_1cta(empty_bar(stage));  // frees the stage once these MMAs have read it
                     if (++stage == STAGES) {
                         stage = 0;

@@ -47,7 +47,9 @@ struct PairSmemLayout {
     static_assert(kDynamicBytes > 116224, "two CTAs could share an SM and contend for TMEM");
 };
 
-template <uint32_t BN, uint32_t KBS, uint32_t STAGES>
+// B_KN: B is given K x N row-major; this CTA's 128-column half of the B tile is loaded as two boxes of
+// {64 columns, 64 k-rows} per k-block and read by the MMA as an MN-major operand.
+template <uint32_t BN, uint32_t KBS, uint32_t STAGES, bool B_KN = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNumThreads, 1)
 gemm_bf16_sm100_2cta(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                      const GemmParams p)
@@ -56,8 +58,9 @@ gemm_bf16_sm100_2cta(const __grid_constant__ CUtensorMap tma_a, const __grid_con
     static_assert(BN == 256, "pair tile is 256 x 256");
     static_assert(KBS == 1 || KBS == 2, "one or two k-blocks per stage");
     constexpr uint32_t kTmemCols = 2 * BN;  // two BN-column accumulator buffers per CTA
-    constexpr uint32_t kIdesc = ptx::make_instr_desc_bf16(kPairBlockM, BN);
+    constexpr uint32_t kIdesc = ptx::make_instr_desc_bf16(kPairBlockM, BN, B_KN);
     constexpr uint32_t kStepK = KBS * kBlockK;
+    constexpr uint32_t kChunkBytes = kBlockK * 128;  // one 64-column chunk of a K x N tile: 64 k-rows x 128 B
 
     extern __shared__ uint8_t smem_raw[];
     // Both CTAs of the pair see the same dynamic shared-memory base offset, so the aligned
@@ -145,7 +148,14 @@ gemm_bf16_sm100_2cta(const __grid_constant__ CUtensorMap tma_a, const __grid_con
                             // a k-block past the end of K is fetched all the same: TMA fills it with zeros
                             const int32_t kx = static_cast<int32_t>((step * KBS + sub) * kBlockK);
                             ptx::tma_load_2d_pair_hint(sa + sub * L::kABytes, &tma_a, leader_full, kx, m0, pol_a);
-                            ptx::tma_load_2d_pair_hint(sb + sub * L::kBBytes, &tma_b, leader_full, kx, n0, pol_b);
+                            if constexpr (B_KN) {
+#pragma unroll
+                                for (uint32_t j = 0; j < BN / 128; ++j)  // x = column, y = k row
+                                    ptx::tma_load_2d_pair_hint(sb + sub * L::kBBytes + j * kChunkBytes, &tma_b, leader_full,
+                                                               n0 + static_cast<int32_t>(64u * j), kx, pol_b);
+                            } else {
+                                ptx::tma_load_2d_pair_hint(sb + sub * L::kBBytes, &tma_b, leader_full, kx, n0, pol_b);
+                            }
                         }
                     }
                     if (++stage == STAGES) {
@@ -190,10 +200,12 @@ gemm_bf16_sm100_2cta(const __grid_constant__ CUtensorMap tma_a, const __grid_con
 #pragma unroll
                     for (uint32_t sub = 0; sub < KBS; ++sub) {
                         const uint64_t da = ptx::make_smem_desc_sw128(sa + sub * L::kABytes);
-                        const uint64_t db = ptx::make_smem_desc_sw128(sb + sub * L::kBBytes);
+                        const uint64_t db = B_KN ? ptx::make_smem_desc_sw128_mn(sb + sub * L::kBBytes, kChunkBytes)
+                                                 : ptx::make_smem_desc_sw128(sb + sub * L::kBBytes);
+                        constexpr uint32_t kStepB = B_KN ? 128u : 2u;  // +2048 B or +32 B per 16-wide K step
 #pragma unroll
                         for (uint32_t k = 0; k < kBlockK / kUmmaK; ++k)
-                            ptx::mma_bf16_2cta(tmem_d, da + 2u * k, db + 2u * k, kIdesc,
+                            ptx::mma_bf16_2cta(tmem_d, da + 2u * k, db + kStepB * k, kIdesc,
                                                (step | sub | k) != 0u ? 1u : 0u);
                     }
                     ptx::mma_commit_2cta_mask(empty_bar(stage), 3);  // stage s of both CTAs is free

@@ -102,6 +102,7 @@ struct maize_ctx {
     cudaEvent_t ev_start = nullptr, ev_done = nullptr;
     cudaEvent_t ev_in[kMaxHostSlabs] = {}, ev_gemm[kMaxHostSlabs] = {};
     bool attr_set[kNumVariants] = {};
+    bool attr_set_kn[kNumVariants] = {};  // the same for the K x N (MN-major B) instantiations
     float *d_partials = nullptr;        // stream-K scratch of the skinny kernels
     unsigned int *d_counters = nullptr;  // arrival counters, zero between launches
     unsigned int *d_push_counter = nullptr;  // [0]: CTA arrivals of the multicast push; [16 + p]: of the scatter per rank
@@ -148,13 +149,14 @@ maize_status_t make_operand_map(maize_ctx_t *ctx, CUtensorMap *map, const void *
 template <typename Kernel>
 maize_status_t launch_kernel(maize_ctx_t *ctx, int variant_index, Kernel kernel, uint32_t smem_bytes,
                              const CUtensorMap &ta, const CUtensorMap &tb, const GemmParams &p, uint32_t grid,
-                             cudaStream_t stream)
+                             cudaStream_t stream, bool b_kn = false)
 {
-    if (!ctx->attr_set[variant_index]) {
+    bool &attr_done = b_kn ? ctx->attr_set_kn[variant_index] : ctx->attr_set[variant_index];
+    if (!attr_done) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
         if (e != cudaSuccess)
             return fail_cuda(ctx, "cudaFuncSetAttribute(max dynamic smem)", e);
-        ctx->attr_set[variant_index] = true;
+        attr_done = true;
     }
     kernel<<<grid, maize::kNumThreads, smem_bytes, stream>>>(ta, tb, p);
     cudaError_t e = cudaGetLastError();
@@ -164,12 +166,12 @@ maize_status_t launch_kernel(maize_ctx_t *ctx, int variant_index, Kernel kernel,
     return MAIZE_OK;
 }
 
-template <uint32_t BN, uint32_t STAGES>
+template <uint32_t BN, uint32_t STAGES, bool B_KN = false>
 maize_status_t launch_variant(maize_ctx_t *ctx, int variant_index, const CUtensorMap &ta, const CUtensorMap &tb,
                               const GemmParams &p, uint32_t grid, cudaStream_t stream)
 {
-    return launch_kernel(ctx, variant_index, maize::gemm_bf16_sm100_1cta<BN, STAGES>,
-                         maize::GemmSmemLayout<BN, STAGES>::kDynamicBytes, ta, tb, p, grid, stream);
+    return launch_kernel(ctx, variant_index, maize::gemm_bf16_sm100_1cta<BN, STAGES, B_KN>,
+                         maize::GemmSmemLayout<BN, STAGES>::kDynamicBytes, ta, tb, p, grid, stream, B_KN);
 }
 
 // Tile width for the pair-split skinny kernel: the narrowest multiple of 32 for which one pair per tile
@@ -275,8 +277,9 @@ maize_status_t launch_skinny(maize_ctx_t *ctx, int vi, const CUtensorMap &tx, co
     return MAIZE_OK;
 }
 
+// b_kn: B is K x N row-major with row pitch ldb (C = A * B) instead of N x K (C = A * B^T).
 maize_status_t gemm_impl(maize_ctx_t *ctx, const void *a, uint64_t lda, const void *b, uint64_t ldb, void *c,
-                         uint64_t ldc, uint32_t m, uint32_t n, uint32_t k, cudaStream_t stream)
+                         uint64_t ldc, uint32_t m, uint32_t n, uint32_t k, cudaStream_t stream, bool b_kn = false)
 {
     if (!ctx)
         return MAIZE_ERR_INVALID_ARG;
@@ -297,16 +300,27 @@ maize_status_t gemm_impl(maize_ctx_t *ctx, const void *a, uint64_t lda, const vo
     }
     if (!a || !b)
         return fail(ctx, MAIZE_ERR_INVALID_ARG, "A or B pointer is null");
-    if (lda < k || ldb < k)
-        return fail(ctx, MAIZE_ERR_INVALID_ARG, "lda/ldb is smaller than K");
-    if (k % 8 != 0 || lda % 8 != 0 || ldb % 8 != 0)
+    if (lda < k || ldb < (b_kn ? n : k))
+        return fail(ctx, MAIZE_ERR_INVALID_ARG, "lda/ldb is smaller than the row length");
+    if (lda % 8 != 0 || ldb % 8 != 0 || (!b_kn && k % 8 != 0))
         return fail(ctx, MAIZE_ERR_UNSUPPORTED, "K, lda and ldb must be multiples of 8 (16-byte TMA row pitch)");
     if (reinterpret_cast<uintptr_t>(a) % 16 != 0 || reinterpret_cast<uintptr_t>(b) % 16 != 0)
         return fail(ctx, MAIZE_ERR_UNSUPPORTED, "A and B must be 16-byte aligned");
     if (lda * 2 >= (1ull << 40) || ldb * 2 >= (1ull << 40))
         return fail(ctx, MAIZE_ERR_UNSUPPORTED, "row pitch beyond the TMA limit of 2^40 bytes");
 
-    const int vi = pick_variant(ctx, m, n, k);
+    int vi = pick_variant(ctx, m, n, k);
+    if (b_kn) {
+        // K x N tiles come in 64-column chunks: the pair kernel or the one-CTA kernels of width >= 64
+        if (ctx->force_kernel != 0) {
+            if (vi == 3 || vi >= kFirstSkinny)
+                return fail(ctx, MAIZE_ERR_UNSUPPORTED, "this kernel variant does not take a K x N matrix B");
+        } else if (vi >= kFirstSkinny) {
+            vi = n > 128 ? 0 : (n > 64 ? 1 : 2);
+        } else if (vi == 3) {
+            vi = 2;
+        }
+    }
     const KernelVariant &kv = kVariants[vi];
 
     if (vi == kSkinnyPair) {
@@ -394,7 +408,8 @@ maize_status_t gemm_impl(maize_ctx_t *ctx, const void *a, uint64_t lda, const vo
     maize_status_t st = make_operand_map(ctx, &ta, a, m, k, lda, maize::kBlockM);
     if (st != MAIZE_OK)
         return st;
-    st = make_operand_map(ctx, &tb, b, n, k, ldb, kv.box_rows_b);
+    st = b_kn ? make_operand_map(ctx, &tb, b, k, n, ldb, maize::kBlockK)  // boxes of 64 columns x 64 k-rows
+              : make_operand_map(ctx, &tb, b, n, k, ldb, kv.box_rows_b);
     if (st != MAIZE_OK)
         return st;
 
@@ -429,6 +444,19 @@ maize_status_t gemm_impl(maize_ctx_t *ctx, const void *a, uint64_t lda, const vo
         cudaMemsetAsync(ctx->d_profile, 0, sizeof(unsigned long long) * maize::kProfileSlots * kMaxProfileCtas, stream);
     }
 
+    if (b_kn) {
+        switch (vi) {
+        case 0: return launch_variant<256, 4, true>(ctx, vi, ta, tb, p, grid, stream);
+        case 1: return launch_variant<128, 6, true>(ctx, vi, ta, tb, p, grid, stream);
+        case 2: return launch_variant<64, 8, true>(ctx, vi, ta, tb, p, grid, stream);
+        case 4:
+            return launch_kernel(ctx, vi, maize::gemm_bf16_sm100_2cta<256, 1, 6, true>,
+                                 maize::PairSmemLayout<256, 1, 6>::kDynamicBytes, ta, tb, p, grid, stream, true);
+        default:
+            return launch_kernel(ctx, vi, maize::gemm_bf16_sm100_2cta<256, 2, 3, true>,
+                                 maize::PairSmemLayout<256, 2, 3>::kDynamicBytes, ta, tb, p, grid, stream, true);
+        }
+    }
     switch (vi) {
     case 0: return launch_variant<256, 4>(ctx, vi, ta, tb, p, grid, stream);
     case 1: return launch_variant<128, 6>(ctx, vi, ta, tb, p, grid, stream);
@@ -581,6 +609,26 @@ maize_status_t maize_gemm_bf16_ld(maize_ctx_t *ctx, const void *a, uint64_t lda,
                                   uint64_t ldc, uint32_t m, uint32_t n, uint32_t k, void *cuda_stream)
 {
     return gemm_impl(ctx, a, lda, b, ldb, c, ldc, m, n, k, static_cast<cudaStream_t>(cuda_stream));
+}
+
+maize_status_t maize_gemm_bf16_kn(maize_ctx_t *ctx, const void *a, uint32_t a_rows, uint32_t a_cols, const void *b,
+                                  uint32_t b_rows, uint32_t b_cols, void *c, uint32_t c_rows, uint32_t c_cols,
+                                  void *cuda_stream)
+{
+    if (!ctx)
+        return MAIZE_ERR_INVALID_ARG;
+    if (a_cols != b_rows)
+        return fail(ctx, MAIZE_ERR_INVALID_ARG, "a_cols != b_rows (both are K; B is stored K x N)");
+    if (c_rows != a_rows || c_cols != b_cols)
+        return fail(ctx, MAIZE_ERR_INVALID_ARG, "C must be a_rows x b_cols");
+    return gemm_impl(ctx, a, a_cols, b, b_cols, c, c_cols, a_rows, b_cols, a_cols, static_cast<cudaStream_t>(cuda_stream),
+                     true);
+}
+
+maize_status_t maize_gemm_bf16_kn_ld(maize_ctx_t *ctx, const void *a, uint64_t lda, const void *b, uint64_t ldb,
+                                     void *c, uint64_t ldc, uint32_t m, uint32_t n, uint32_t k, void *cuda_stream)
+{
+    return gemm_impl(ctx, a, lda, b, ldb, c, ldc, m, n, k, static_cast<cudaStream_t>(cuda_stream), true);
 }
 
 maize_status_t maize_gemm_bf16_host(maize_ctx_t *ctx, const void *a_host, uint32_t a_rows, uint32_t a_cols,

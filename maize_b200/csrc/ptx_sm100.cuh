@@ -294,12 +294,31 @@ __device__ __forceinline__ uint64_t make_smem_desc_sw128(uint32_t smem_addr)
     return d;
 }
 
+// Shared-memory matrix descriptor for an MN-major bf16 operand (the matrix is stored with its M or N index
+// contiguous, e.g. B given as K x N row-major).  The tile is a row of chunks; a chunk is 64 MN-elements
+// (128 bytes) wide and holds the tile's K rows one after the other, as a TMA box {64 elements, K rows} with
+// the 128-byte swizzle writes it:
+//   leading-dimension byte offset  = distance between consecutive 64-element chunks along MN (`chunk_bytes`)
+//   stride-dimension byte offset   = distance between consecutive groups of 8 K rows = 8 x 128 B = 1024 B
+// A K step of 16 elements is two such groups: the start address advances by 2048 bytes.
+__device__ __forceinline__ uint64_t make_smem_desc_sw128_mn(uint32_t smem_addr, uint32_t chunk_bytes)
+{
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
+    d |= static_cast<uint64_t>((chunk_bytes >> 4) & 0x3FFFu) << 16;
+    d |= static_cast<uint64_t>(1024 >> 4) << 32;
+    d |= static_cast<uint64_t>(1) << 46;
+    d |= static_cast<uint64_t>(2) << 61;
+    return d;
+}
+
 // Instruction descriptor for kind::f16 with bf16 A/B (both K-major), fp32 D:
 //   bits 4-5 D format (1 = f32), 7-9 A format (1 = bf16), 10-12 B format (1 = bf16),
 //   bit 15/16 A/B major (0 = K), bits 17-22 N >> 3, bits 24-28 M >> 4.
-__host__ __device__ constexpr uint32_t make_instr_desc_bf16(uint32_t mma_m, uint32_t mma_n)
+__host__ __device__ constexpr uint32_t make_instr_desc_bf16(uint32_t mma_m, uint32_t mma_n, bool b_mn_major = false)
 {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((mma_n >> 3) << 17) | ((mma_m >> 4) << 24);
+    return (1u << 4) | (1u << 7) | (1u << 10) | (b_mn_major ? (1u << 16) : 0u) | ((mma_n >> 3) << 17) |
+           ((mma_m >> 4) << 24);
 }
 
 // D[tmem] (+)= A[smem] * B[smem]^T, one CTA.  Issued by ONE thread.

@@ -185,6 +185,28 @@ class Context:
     def flag_store(self, flag_ptr: int, value: int, stream=None) -> None:
         self._check(self._lib.maize_flag_store(self._h, flag_ptr, value & 0xFFFFFFFF, _stream_handle(stream)))
 
+    def gemm_kn(self, a, b, out=None, stream=None):
+        """``out = a @ b`` for bf16 CUDA tensors with b given K x N (N contiguous), the layout the reference's
+        demo walks; rows may be strided."""
+        import torch
+        for name, t in (("a", a), ("b", b)):
+            if t.dim() != 2 or t.dtype != torch.bfloat16 or not t.is_cuda or (t.shape[1] > 1 and t.stride(1) != 1):
+                raise MaizeError(_ffi.INVALID_ARG, f"{name}: expected a 2-D bfloat16 CUDA tensor with unit column stride")
+        m, k = a.shape
+        kb, n = b.shape
+        if k != kb:
+            raise MaizeError(_ffi.INVALID_ARG, "a.shape[1] != b.shape[0] (b is stored K x N)")
+        if out is None:
+            out = torch.empty((m, n), dtype=torch.bfloat16, device=a.device)
+        elif out.shape != (m, n) or out.dtype != torch.bfloat16 or not out.is_cuda or (n > 1 and out.stride(1) != 1):
+            raise MaizeError(_ffi.INVALID_ARG, "out: expected an M x N bfloat16 CUDA tensor with unit column stride")
+        lda = a.stride(0) if m > 1 else max(k, 8)
+        ldb = b.stride(0) if k > 1 else max(n, 8)
+        ldc = out.stride(0) if m > 1 else max(n, 1)
+        self._check(self._lib.maize_gemm_bf16_kn_ld(self._h, a.data_ptr(), lda, b.data_ptr(), ldb, out.data_ptr(), ldc,
+                                                    m, n, k, _stream_handle(stream)))
+        return out
+
     def debug_wait_expires(self, budget_ns: int, stream=None) -> None:
         self._check(self._lib.maize_debug_wait_expires(self._h, int(budget_ns), _stream_handle(stream)))
 

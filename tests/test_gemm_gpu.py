@@ -129,6 +129,46 @@ def test_forced_skinny_rejects_tall_a(ctx):
         ctx.set("force_kernel", 0)
 
 
+@pytest.mark.parametrize("force", [0, 1, 2, 3, 5, 6])
+@pytest.mark.parametrize("m,n,k", [
+    (128, 256, 64), (128, 256, 64 * 9), (256, 512, 256), (300, 1000, 136), (513, 264, 1032), (7, 8, 16),
+    (130, 248, 72), (1280, 2304, 256), (2000, 24, 512), (64, 4096, 100),
+])
+def test_b_stored_k_by_n(ctx, oracle, m, n, k, force):
+    """B given K x N row-major (the reference demo's layout): loaded as 64-column boxes, MN-major MMA operand.
+    N must be a multiple of 8 (row pitch); K is free."""
+    import torch
+    a = oracle.fill_bf16(29, 0, (m, k))
+    b_nk = oracle.fill_bf16(29, 1, (n, k))
+    ref = oracle.gemm_bf16(a, b_nk)
+    da = to_device(a)
+    db_kn = to_device(np.ascontiguousarray(b_nk.T))  # K x N
+    lda_pad = (k + 7) // 8 * 8
+    if lda_pad != k:  # A's row pitch must be a multiple of 8 elements: embed A in a padded buffer
+        buf = torch.zeros((m, lda_pad), dtype=torch.bfloat16, device="cuda")
+        buf[:, :k] = da
+        da = buf[:, :k]
+    dc = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+    ctx.set("force_kernel", force)
+    try:
+        ctx.gemm_kn(da, db_kn, out=dc)
+        ctx.poll()
+    finally:
+        ctx.set("force_kernel", 0)
+    assert_parity(oracle, to_host(dc), ref, k, oracle.max_abs_bf16(a), oracle.max_abs_bf16(b_nk),
+                  f"K x N B, {m}x{n}x{k}, kernel {force}")
+
+
+def test_b_k_by_n_full_config(ctx, oracle):
+    """Config c1 (4096^3, the reference demo's own size) with B in the demo's K x N layout."""
+    m = n = k = 4096
+    a = oracle.fill_bf16(0, 0, (m, k))
+    b_nk = oracle.fill_bf16(0, 1, (n, k))
+    dc = ctx.gemm_kn(to_device(a), to_device(np.ascontiguousarray(b_nk.T)))
+    ctx.poll()
+    assert_parity(oracle, to_host(dc), oracle.gemm_bf16(a, b_nk), k, oracle.max_abs_bf16(a), oracle.max_abs_bf16(b_nk))
+
+
 def test_canaries_around_c(ctx, oracle):
     """Nothing is written outside C: rows of padding between C rows (ldc > N) and guard bands stay intact."""
     import torch
