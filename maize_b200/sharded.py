@@ -265,6 +265,24 @@ class NShardedGemm:
         self.step += 1
         return c_shard
 
+    def gather_c(self, c_shard):
+        """Dense M x N matrix C on every rank from the column blocks (for callers that do not want C sharded).
+        The hot path keeps C sharded; this is a convenience on top of ``all_gather``."""
+        import torch
+        if self.world == 1:
+            return c_shard
+        widest = shard_bounds(self.n, self.world, 0)
+        width = widest[1] - widest[0]
+        padded = c_shard
+        if c_shard.shape[1] != width:
+            padded = torch.zeros((self.m, width), dtype=c_shard.dtype, device=c_shard.device)
+            padded[:, :c_shard.shape[1]] = c_shard
+        parts = [torch.empty_like(padded) for _ in range(self.world)]
+        self.dist.all_gather(parts, padded.contiguous(), group=self.group)
+        cols = [parts[r][:, :shard_bounds(self.n, self.world, r)[1] - shard_bounds(self.n, self.world, r)[0]]
+                for r in range(self.world)]
+        return torch.cat(cols, dim=1)
+
     def run(self, a_root, b_shard, c_shard):
         """One step: replicate A from the root slab by slab and multiply as slabs arrive.
 

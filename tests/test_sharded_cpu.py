@@ -83,6 +83,9 @@ def _worker(rank, world, port, m, n, k, out_dir):
         for _ in range(2):  # twice: the landing buffer is reused
             op.run(a_root, b_shard, c_shard)
         np.save(os.path.join(out_dir, f"c{rank}.npy"), as_u16(c_shard))
+        dense = op.gather_c(c_shard)
+        assert dense.shape == (m, n)
+        np.save(os.path.join(out_dir, f"dense{rank}.npy"), as_u16(dense))
     finally:
         dist.destroy_process_group()
 
@@ -94,3 +97,5 @@ def test_two_rank_sharded_gemm_matches_unsharded(tmp_path, oracle):
     ref = oracle.gemm_bf16(oracle.fill_bf16(21, 0, (m, k)), oracle.fill_bf16(21, 1, (n, k)))
     got = np.concatenate([np.load(tmp_path / f"c{r}.npy") for r in range(world)], axis=1)
     assert np.array_equal(got, ref)
+    for r in range(world):  # the all-gathered dense C is the same on every rank (uneven shards: 72 + 71 columns)
+        assert np.array_equal(np.load(tmp_path / f"dense{r}.npy"), ref)
