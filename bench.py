@@ -62,6 +62,8 @@ def parse_args():
     p.add_argument("--e2e-steps", type=int, default=3)
     p.add_argument("--b-layout", default="nk", choices=["nk", "kn"],
                    help="nk: B stored N x K (the bench's contract); kn: B stored K x N as the reference demo walks it (N = 1 GPU only)")
+    p.add_argument("--no-pdl", action="store_true",
+                   help="c3 only: do not use programmatic dependent launch with static weights for the decode kernel")
     p.add_argument("--no-cpu-baseline", action="store_true")
     p.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (for profiler captures)")
     p.add_argument("--force-kernel", type=int, default=0, help="kernel variant id (0 = the library's heuristic)")
@@ -230,6 +232,11 @@ def main():
     ctx = maize_b200.Context(local_rank)
     if args.force_kernel:
         ctx.set("force_kernel", args.force_kernel)
+    decode_pdl = args.workload == "c3" and not args.no_pdl
+    if decode_pdl:
+        # decode: B holds weights that nothing in the stream writes, so consecutive launches may overlap
+        ctx.set("pdl", 1)
+        ctx.set("b_static", 1)
     gen = torch.Generator(device=dev)
     gen.manual_seed(seed)  # every rank draws the same A; B rows are taken from a per-rank stream
 
@@ -416,7 +423,8 @@ def main():
                                          else "NCCL broadcast"),
                        "l2": (f"rotating over {n_sets} independent input sets ({n_sets * rank_bytes >> 20} MiB > 4x L2), "
                               "back-to-back launches") if small else "inputs exceed L2 (back-to-back launches)",
-                       "algorithmic_bytes": total_bytes, "ms_per_step_by_rank": per_rank_ms},
+                       "algorithmic_bytes": total_bytes, "ms_per_step_by_rank": per_rank_ms,
+                       "launch": "programmatic dependent launch, B declared static (weights)" if decode_pdl else "plain"},
             "roofline": roof, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
         }
         print(json.dumps(line), flush=True)

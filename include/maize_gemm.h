@@ -155,7 +155,10 @@ MAIZE_API maize_status_t maize_ctx_poll(maize_ctx_t *ctx, void *cuda_stream);
  * see maize_kernel_name), "max_ctas" (cap on the persistent grid, 0 = SM count),
  * "profile" (1 = per-CTA cycle accounting, see maize_ctx_read_profile), "group_rows" (rows of A
  * whose tiles are scheduled together, default 2048), "push_threads" (threads per CTA of the copy
- * kernels of the multi-GPU path, default 512), "debug_flags"
+ * kernels of the multi-GPU path, default 512), "pdl" (1 = launch the decode kernel with programmatic
+ * stream serialization, so that it may start while the stream's previous kernel drains), "b_static"
+ * (1 = the caller guarantees that no earlier work of the stream writes B, e.g. inference weights; with
+ * "pdl" the kernel then fetches its first B tiles before waiting for that earlier work), "debug_flags"
  * (performance diagnostics that make results WRONG: 1 = all loads hit one tile, 2 = no loads). */
 MAIZE_API maize_status_t maize_ctx_set(maize_ctx_t *ctx, const char *key, int64_t value);
 MAIZE_API maize_status_t maize_ctx_get(const maize_ctx_t *ctx, const char *key, int64_t *value);

@@ -32,6 +32,12 @@ struct SkinnyPairParams {
     uint32_t bn;       // tile width: rows of B per tile, multiple of 32, 32..256
     uint32_t tiles_n;  // ceil(N / bn)
     uint32_t num_kb;   // ceil(K / 64)
+    // Launched with programmatic stream serialization: the kernel may start before the previous kernel of the
+    // stream has finished and orders itself with griddepcontrol.wait.  With b_static (the caller guarantees
+    // that no earlier work of the stream writes B, e.g. inference weights) the first lap of B loads is issued
+    // BEFORE that wait, so the weights stream in while the previous kernel drains.
+    uint32_t pdl;
+    uint32_t b_static;
 };
 
 __device__ __forceinline__ void st_shared_cluster_v4(uint32_t cluster_addr, float a, float b, float c, float d)
@@ -82,16 +88,25 @@ gemm_bf16_sm100_skinny_pair(const __grid_constant__ CUtensorMap tma_x /* A: M x 
     // flight while TMEM is being allocated.
     uint32_t pr_stage = 0, pr_phase = 0, pr_kb = kb_lo;
     uint64_t pol_stream = 0, pol_keep = 0;
-    auto issue_kb = [&](uint32_t kb, uint32_t stage) {
-        const uint32_t sx = smem_base + stage * L::kStageBytes;
-        const uint32_t sw = sx + L::kXBytes;
-        const int32_t kx = static_cast<int32_t>(kb * kBlockK);
+    auto issue_w = [&](uint32_t kb, uint32_t stage) {  // B tile of one k-block (and the stage's byte count)
+        const uint32_t sw = smem_base + stage * L::kStageBytes + L::kXBytes;
         ptx::mbar_arrive_expect_tx(full_bar(stage), stage_tx);
-        ptx::tma_load_2d_hint(sw, &tma_w, full_bar(stage), kx, static_cast<int32_t>(t * p.bn), pol_stream);
-#pragma unroll
-        for (uint32_t q = 0; q < 4; ++q)  // the same 32 rows of A into each quarter of the tile
-            ptx::tma_load_2d_hint(sx + q * (L::kXBytes / 4), &tma_x, full_bar(stage), kx, 0, pol_keep);
+        ptx::tma_load_2d_hint(sw, &tma_w, full_bar(stage), static_cast<int32_t>(kb * kBlockK),
+                              static_cast<int32_t>(t * p.bn), pol_stream);
     };
+    auto issue_x = [&](uint32_t kb, uint32_t stage) {  // the same 32 rows of A into each quarter of the A tile
+        const uint32_t sx = smem_base + stage * L::kStageBytes;
+#pragma unroll
+        for (uint32_t q = 0; q < 4; ++q)
+            ptx::tma_load_2d_hint(sx + q * (L::kXBytes / 4), &tma_x, full_bar(stage),
+                                  static_cast<int32_t>(kb * kBlockK), 0, pol_keep);
+    };
+    auto issue_kb = [&](uint32_t kb, uint32_t stage) {
+        issue_w(kb, stage);
+        issue_x(kb, stage);
+    };
+    const bool early_b = p.pdl != 0u && p.b_static != 0u;  // B may be fetched before the dependency wait
+    uint32_t prefilled = 0;                                // stages whose B load was issued early
 
     if (threadIdx.x == 0) {
         ptx::prefetch_tensormap(&tma_w);
@@ -105,9 +120,16 @@ gemm_bf16_sm100_skinny_pair(const __grid_constant__ CUtensorMap tma_x /* A: M x 
         ptx::fence_barrier_init();
         pol_stream = ptx::policy_evict_first();
         pol_keep = ptx::policy_evict_last();
-        if (have_tile) {
+        if (p.pdl)
+            ptx::grid_dependency_launch_dependents();  // the next kernel may be scheduled as SMs free up
+        if (have_tile && (early_b || !p.pdl)) {
             for (uint32_t s = 0; s < STAGES && pr_kb < kb_hi; ++s) {  // first lap: every stage is free
-                issue_kb(pr_kb++, pr_stage);
+                if (early_b) {
+                    issue_w(pr_kb++, pr_stage);  // A follows after the dependency wait
+                    ++prefilled;
+                } else {
+                    issue_kb(pr_kb++, pr_stage);
+                }
                 if (++pr_stage == STAGES) {
                     pr_stage = 0;
                     pr_phase ^= 1u;
@@ -123,10 +145,14 @@ gemm_bf16_sm100_skinny_pair(const __grid_constant__ CUtensorMap tma_x /* A: M x 
     __syncthreads();
     ptx::tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    if (p.pdl)
+        ptx::grid_dependency_wait();  // everything below may read A and write C
 
     if (warp == 0) {
         // ------------------------------------------------------- TMA producer --
         if (lane == 0 && have_tile) {
+            for (uint32_t s = 0; s < prefilled; ++s)  // the A tiles of the stages whose B was fetched early
+                issue_x(kb_lo + s, s);
             while (pr_kb < kb_hi) {
                 if (!wait_bounded(empty_bar(pr_stage), pr_phase ^ 1u, ctl, 1))
                     break;

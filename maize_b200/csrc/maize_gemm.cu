@@ -92,6 +92,8 @@ struct maize_ctx {
     int max_ctas = 0;
     uint32_t debug_flags = 0;
     uint32_t group_rows = 2048;
+    uint32_t pdl = 0;       // launch the decode kernel with programmatic stream serialization
+    uint32_t b_static = 0;  // the caller guarantees that nothing earlier in the stream writes B (weights)
     uint32_t push_threads = 512;  // threads per CTA of the copy kernels of the multi-GPU path
     uint64_t launches = 0;
     EncodeTiledFn encode = nullptr;
@@ -362,8 +364,25 @@ maize_status_t gemm_impl(maize_ctx_t *ctx, const void *a, uint64_t lda, const vo
                 return fail_cuda(ctx, "cudaFuncSetAttribute(max dynamic smem)", ea);
             ctx->attr_set[vi] = true;
         }
-        kernel<<<2 * pp.tiles_n, maize::kNumThreads, maize::SkinnySmemLayout<4>::kDynamicBytes, stream>>>(tx, tw, pp);
-        cudaError_t el = cudaGetLastError();
+        pp.pdl = ctx->pdl;
+        pp.b_static = ctx->b_static;
+        cudaError_t el;
+        if (ctx->pdl) {
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3(2 * pp.tiles_n);
+            cfg.blockDim = dim3(maize::kNumThreads);
+            cfg.dynamicSmemBytes = maize::SkinnySmemLayout<4>::kDynamicBytes;
+            cfg.stream = stream;
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attr[0].val.programmaticStreamSerializationAllowed = 1;
+            cfg.attrs = attr;
+            cfg.numAttrs = 1;
+            el = cudaLaunchKernelEx(&cfg, kernel, tx, tw, pp);
+        } else {
+            kernel<<<2 * pp.tiles_n, maize::kNumThreads, maize::SkinnySmemLayout<4>::kDynamicBytes, stream>>>(tx, tw, pp);
+            el = cudaGetLastError();
+        }
         if (el != cudaSuccess)
             return fail_cuda(ctx, "kernel launch", el);
         ctx->launches += 1;
@@ -787,6 +806,10 @@ maize_status_t maize_ctx_set(maize_ctx_t *ctx, const char *key, int64_t value)
         if (value < 128 || value > (1 << 24))
             return fail(ctx, MAIZE_ERR_INVALID_ARG, "group_rows out of range");
         ctx->group_rows = static_cast<uint32_t>(value);
+    } else if (!strcmp(key, "pdl")) {
+        ctx->pdl = value ? 1u : 0u;
+    } else if (!strcmp(key, "b_static")) {
+        ctx->b_static = value ? 1u : 0u;
     } else if (!strcmp(key, "push_threads")) {
         if (value < 32 || value > 512 || value % 32 != 0)
             return fail(ctx, MAIZE_ERR_INVALID_ARG, "push_threads: a multiple of 32 in [32, 512]");

@@ -421,6 +421,19 @@ __device__ __forceinline__ uint32_t pack_bf16x2(uint32_t lo_f32_bits, uint32_t h
     return d;
 }
 
+// Programmatic dependent launch.  launch_dependents: this CTA no longer objects to the next kernel of the
+// stream being scheduled (it starts on SMs as they free up).  wait: block until every kernel this one
+// depends on has completed and its memory is visible; a no-op when the launch carried no such dependency.
+__device__ __forceinline__ void grid_dependency_launch_dependents()
+{
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+__device__ __forceinline__ void grid_dependency_wait()
+{
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
 __device__ __forceinline__ void cluster_arrive()
 {
     asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");

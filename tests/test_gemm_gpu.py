@@ -92,6 +92,35 @@ def test_skinny_pair_split(ctx, oracle, m, n, k):
     run_case(ctx, oracle, m, n, k, seed=28, force=9)
 
 
+def test_skinny_pair_with_dependent_launch(ctx, oracle):
+    """Back-to-back decode launches with programmatic dependent launch: A of launch i+1 is produced by a kernel
+    that runs between the GEMMs, so the dependency wait is what keeps the result right; B is declared static."""
+    import torch
+    m, n, k = 16, 16384, 1024
+    a, b = make_inputs(oracle, m, n, k, 30, scale_b=0.05)
+    da, db = to_device(a), to_device(b)
+    ref1 = oracle.gemm_bf16(a, b)
+    a2 = oracle.f32_to_bf16(oracle.bf16_to_f32(a) * 2.0)
+    ref2 = oracle.gemm_bf16(a2, b)
+    ctx.set("pdl", 1)
+    ctx.set("b_static", 1)
+    try:
+        outs = []
+        x = da.clone()
+        for i in range(6):
+            c = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+            ctx.gemm(x, db, out=c)
+            outs.append(c)
+            x = da * 2 if i % 2 == 0 else da.clone()  # the next launch's A comes from a kernel in between
+        ctx.poll()
+    finally:
+        ctx.set("pdl", 0)
+        ctx.set("b_static", 0)
+    for i, c in enumerate(outs):
+        ref = ref1 if i % 2 == 0 else ref2
+        assert_parity(oracle, to_host(c), ref, k, 2 * oracle.max_abs_bf16(a), oracle.max_abs_bf16(b), f"launch {i}")
+
+
 def test_skinny_pair_rejects_more_than_one_wave(ctx):
     import torch
     import maize_b200
