@@ -54,7 +54,7 @@ def parse_args():
     p.add_argument("--impl", default="ours", choices=["ours", "reference"])
     p.add_argument("--slabs", type=int, default=0,
                    help="row slabs of A for the overlapped broadcast (N > 1); 0 = sizes from the makespan model")
-    p.add_argument("--transport", default="auto", choices=["auto", "multimem", "nccl"],
+    p.add_argument("--transport", default="auto", choices=["auto", "multimem", "chain", "nccl"],
                    help="how A reaches the other GPUs at N > 1 (auto: NVSwitch multicast push when available)")
     p.add_argument("--mc-stages", type=int, default=1, choices=[1, 2],
                    help="multimem transport: 2 = root scatters chunks and every GPU multicasts its own, 1 = root multicasts all")
@@ -419,8 +419,9 @@ def main():
                                  "A MxK row-major, B NxK K-major, C MxN bf16",
                        "parallelism": "single GPU" if world == 1 else
                                       f"N-sharded x{world}, A replicated from rank 0 in {len(op.slabs)} row slabs over "
-                                      + ("NVSwitch multicast (multimem.st push kernel)" if op.transport == "multimem"
-                                         else "NCCL broadcast"),
+                                      + {"multimem": "NVSwitch multicast (multimem.st push kernel)",
+                                         "chain": "a copy-engine chain (rank r forwards to r+1 in 1024-row chunks)",
+                                         "nccl": "NCCL broadcast"}[op.transport],
                        "l2": (f"rotating over {n_sets} independent input sets ({n_sets * rank_bytes >> 20} MiB > 4x L2), "
                               "back-to-back launches") if small else "inputs exceed L2 (back-to-back launches)",
                        "algorithmic_bytes": total_bytes, "ms_per_step_by_rank": per_rank_ms,

@@ -210,6 +210,10 @@ MAIZE_API maize_status_t maize_mc_push_after(maize_ctx_t *ctx, const void *wait_
 MAIZE_API maize_status_t maize_scatter_push(maize_ctx_t *ctx, const void *src, void *const *peer_dst,
                                             void *const *peer_flag, uint32_t world, uint32_t root, uint64_t bytes,
                                             uint32_t flag_value, int ctas, void *cuda_stream);
+/* Enqueue a device-to-device copy (copy engines; `dst` may be a peer-mapped address: the bytes then cross
+ * NVLink without any SM taking part).  Building block of the "chain" transport of the N-sharded path. */
+MAIZE_API maize_status_t maize_copy_async(maize_ctx_t *ctx, void *dst, const void *src, uint64_t bytes,
+                                          void *cuda_stream);
 MAIZE_API maize_status_t maize_flags_wait(maize_ctx_t *ctx, const void *flags, uint32_t count, uint32_t value,
                                           void *cuda_stream);
 MAIZE_API maize_status_t maize_flag_store(maize_ctx_t *ctx, void *flag, uint32_t value, void *cuda_stream);

@@ -214,28 +214,21 @@ int pick_variant(const maize_ctx_t *ctx, uint32_t m, uint32_t n, uint32_t k)
     }
     if (m <= 128 && (uint64_t(n) + 255) / 256 < 2ull * sms)
         return kFirstSkinny + 1;
-    // Widest tile whose tile count still fills the machine reasonably; narrow N gets narrow tiles.
+    // A tcgen05.mma costs the same whatever its N, so the tile is as wide as N allows: 32 / 64 / 128 wide only
+    // when N itself is that narrow, otherwise 256.  Between one CTA per 128 x 256 tile and a CTA pair per
+    // 256 x 256 tile (same work per CTA and per tile time, a third less operand traffic for the pair) the
+    // number of waves decides; ties go to the pair.
     if (n <= 32)
         return 3;
     if (n <= 64)
         return 2;
-    // Enough 256 x 256 tiles for every CTA pair: the pair kernel moves a third less data per SM.
-    const uint64_t pair_tiles = ((uint64_t(m) + 255) / 256) * ((uint64_t(n) + 255) / 256);
-    if (m > 128 && n > 128 && pair_tiles >= sms / 2)
-        return kPairWide;
-    const uint64_t tiles256 = tiles_m * ((n + 255) / 256);
-    if (n > 128 && tiles256 >= 2ull * sms)
-        return 0;
-    const uint64_t tiles128 = tiles_m * ((n + 127) / 128);
-    if (n > 128 && tiles256 >= sms) {
-        // between one and two waves of 128x256 tiles: compare wave efficiency with 128x128
-        const double eff256 = double(tiles256) / double(((tiles256 + sms - 1) / sms) * sms);
-        const double eff128 = double(tiles128) / double(((tiles128 + sms - 1) / sms) * sms);
-        return eff256 + 0.05 >= eff128 ? 0 : 1;
-    }
-    if (tiles128 >= sms || n > 64)
+    if (n <= 128)
         return 1;
-    return 2;
+    const uint64_t tiles_n = (uint64_t(n) + 255) / 256;
+    const uint64_t pairs = sms / 2 ? sms / 2 : 1;
+    const uint64_t waves_pair = (((uint64_t(m) + 255) / 256) * tiles_n + pairs - 1) / pairs;
+    const uint64_t waves_single = (tiles_m * tiles_n + sms - 1) / sms;
+    return waves_pair <= waves_single ? kPairWide : 0;
 }
 
 template <bool REPL, uint32_t STAGES>
@@ -941,6 +934,22 @@ maize_status_t maize_scatter_push(maize_ctx_t *ctx, const void *src, void *const
     if (e != cudaSuccess)
         return fail_cuda(ctx, "kernel launch", e);
     ctx->launches += 1;
+    return MAIZE_OK;
+}
+
+maize_status_t maize_copy_async(maize_ctx_t *ctx, void *dst, const void *src, uint64_t bytes, void *cuda_stream)
+{
+    if (!ctx)
+        return MAIZE_ERR_INVALID_ARG;
+    if (bytes == 0)
+        return MAIZE_OK;
+    if (!dst || !src)
+        return fail(ctx, MAIZE_ERR_INVALID_ARG, "null pointer");
+    DeviceGuard guard(ctx->device);
+    // device-to-device; with a peer-mapped destination the copy engines move the bytes over NVLink, no SM involved
+    cudaError_t e = cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, static_cast<cudaStream_t>(cuda_stream));
+    if (e != cudaSuccess)
+        return fail_cuda(ctx, "cudaMemcpyAsync", e);
     return MAIZE_OK;
 }
 

@@ -179,6 +179,10 @@ class Context:
         self._check(self._lib.maize_scatter_push(self._h, src_ptr, dst, flg, world, root, nbytes,
                                                  flag_value & 0xFFFFFFFF, ctas, _stream_handle(stream)))
 
+    def copy_async(self, dst_ptr: int, src_ptr: int, nbytes: int, stream=None) -> None:
+        """Device-to-device copy on the copy engines; dst may be a peer-mapped address."""
+        self._check(self._lib.maize_copy_async(self._h, dst_ptr, src_ptr, nbytes, _stream_handle(stream)))
+
     def flags_wait(self, flags_ptr: int, count: int, value: int, stream=None) -> None:
         self._check(self._lib.maize_flags_wait(self._h, flags_ptr, count, value & 0xFFFFFFFF, _stream_handle(stream)))
 

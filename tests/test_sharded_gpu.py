@@ -50,7 +50,7 @@ def _worker(rank, world, port, transport, m, n, k, steps, out_dir):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("transport", ["nccl", "multimem"])
+@pytest.mark.parametrize("transport", ["nccl", "multimem", "chain"])
 def test_two_gpu_sharded_gemm(tmp_path, oracle, transport):
     import torch
     import torch.multiprocessing as mp
