@@ -1,5 +1,5 @@
 // Inline-PTX wrappers for the sm_100a features the GEMM kernels use: mbarrier,
-// TMA tiled loads and stores (every CTA issues its own), tcgen05 MMA / TMEM.
+// TMA tiled loads (every CTA issues its own), tcgen05 MMA / TMEM, cluster and grid-dependency control.
 //
 // These take the place of the instruction emitters the reference drives through
 // LLVM: cp.async + commit/wait groups (crates/maize_core/src/intrinsics/cuda/cp_async.rs:54-65),
@@ -16,13 +16,6 @@ namespace ptx {
 __device__ __forceinline__ uint32_t smem_u32(const void *p)
 {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
-}
-
-__device__ __forceinline__ uint32_t lane_id()
-{
-    uint32_t l;
-    asm volatile("mov.u32 %0, %%laneid;" : "=r"(l));
-    return l;
 }
 
 __device__ __forceinline__ uint64_t global_timer_ns()
@@ -52,11 +45,6 @@ __device__ __forceinline__ void fence_barrier_init()
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 }
 
-__device__ __forceinline__ void fence_proxy_async_smem()
-{
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-}
-
 __device__ __forceinline__ void mbar_arrive(uint32_t bar)
 {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
@@ -65,19 +53,6 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar)
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes)
 {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-
-// Arrive on the barrier at the same shared offset in CTA `cta_rank` of the cluster.
-__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar, uint32_t cta_rank)
-{
-    asm volatile(
-        "{\n\t"
-        ".reg .b32 remote;\n\t"
-        "mapa.shared::cluster.u32 remote, %0, %1;\n\t"
-        "mbarrier.arrive.release.cluster.shared::cluster.b64 _, [remote];\n\t"
-        "}" ::"r"(bar),
-        "r"(cta_rank)
-        : "memory");
 }
 
 // One probe of the phase with parity `parity`; may suspend for a hardware-defined
@@ -198,34 +173,6 @@ __device__ __forceinline__ uint64_t policy_evict_normal()
     uint64_t p;
     asm volatile("createpolicy.fractional.L2::evict_normal.b64 %0, 1.0;" : "=l"(p));
     return p;
-}
-
-// 2-D tiled store shared -> global (clipped at the tensor's edges).  x must keep
-// x * 2 bytes a multiple of 16 and must not be negative.
-__device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, uint32_t smem_src, int32_t x, int32_t y)
-{
-    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
-                     reinterpret_cast<uint64_t>(map)),
-                 "r"(smem_src), "r"(x), "r"(y)
-                 : "memory");
-}
-
-__device__ __forceinline__ void tma_store_commit()
-{
-    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-}
-
-// Wait until at most N committed store groups still READ shared memory.
-template <int N>
-__device__ __forceinline__ void tma_store_wait_read()
-{
-    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
-}
-
-template <int N>
-__device__ __forceinline__ void tma_store_wait_all()
-{
-    asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
 }
 
 // ----------------------------------------------------------------- tcgen05 --
@@ -393,17 +340,6 @@ __device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)
           "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
           "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
           "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr)
-        : "memory");
-}
-
-__device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&r)[16])
-{
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
         : "r"(taddr)
         : "memory");
 }

@@ -93,3 +93,25 @@ def test_tile_descriptors_keep_reference_names():
     assert repr(t) == "Tile(shape=(128, 64), dtype=BF16)" and t.nbytes() == 16384
     with pytest.raises(TypeError):
         Tile((128, 64), DType.BF16)
+
+
+def test_kernel_selection_table():
+    """The shape -> kernel heuristic, asked without a context (148 SMs assumed): 256-wide tiles whenever N allows,
+    pair or single CTA by whole waves, narrow tiles only for narrow N, the decode kernels for M <= 128."""
+    from maize_b200 import _ffi
+    lib = _ffi.load()
+
+    def pick(m, n, k):
+        return lib.maize_kernel_name(lib.maize_pick_kernel(None, m, n, k)).decode()
+
+    assert pick(16384, 16384, 16384) == "sm100_2cta_256x256x128_s3"
+    assert pick(4096, 4096, 4096) == "sm100_2cta_256x256x128_s3"
+    assert pick(4111, 3967, 4104) == "sm100_2cta_256x256x128_s3"
+    assert pick(2304, 2048, 16384) == "sm100_2cta_256x256x128_s3"   # one wave either way: the pair wins ties
+    assert pick(384, 19000, 4096) == "sm100_1cta_128x256x64_s4"     # 225 single tiles: 2 waves; 150 pair tiles: 3
+    assert pick(4096, 128, 4096) == "sm100_1cta_128x128x64_s6"
+    assert pick(4096, 64, 4096) == "sm100_1cta_128x64x64_s8"
+    assert pick(4096, 24, 4096) == "sm100_1cta_128x32x64_s8"
+    assert pick(16, 16384, 4096) == "sm100_skinny_pair_m32_128xNx64_s4"
+    assert pick(16, 300000, 64) == "sm100_skinny_m32_128x256x64_s4"  # more than one wave of pairs: stream-K
+    assert pick(100, 4096, 4096) == "sm100_skinny_m128_128x256x64_s4"
