@@ -58,6 +58,9 @@ def parse_args():
                    help="how A reaches the other GPUs at N > 1 (auto: NVSwitch multicast push when available)")
     p.add_argument("--mc-stages", type=int, default=1, choices=[1, 2],
                    help="multimem transport: 2 = root scatters chunks and every GPU multicasts its own, 1 = root multicasts all")
+    p.add_argument("--chain-rows", type=int, default=1024, help="chain transport: rows of A per forwarded chunk")
+    p.add_argument("--chain-in-library", action="store_true",
+                   help="chain transport: enqueue a step's forwarding with one library call instead of per-chunk calls")
     p.add_argument("--push-ctas", type=int, default=0, help="CTAs of the multicast push kernel (0 = library default)")
     p.add_argument("--e2e-steps", type=int, default=3)
     p.add_argument("--b-layout", default="nk", choices=["nk", "kn"],

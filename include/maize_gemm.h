@@ -214,6 +214,14 @@ MAIZE_API maize_status_t maize_scatter_push(maize_ctx_t *ctx, const void *src, v
  * NVLink without any SM taking part).  Building block of the "chain" transport of the N-sharded path. */
 MAIZE_API maize_status_t maize_copy_async(maize_ctx_t *ctx, void *dst, const void *src, uint64_t bytes,
                                           void *cuda_stream);
+/* One step of a rank's part in the chain: cut `total_bytes` at `src` into chunks of `chunk_bytes`; for chunk i
+ * (i = 0, 1, ...) wait (bounded, if `wait_flag` is not NULL) until the local word `wait_flag` has reached
+ * first_value + i, copy the chunk to `dst` + its offset (copy engines; `dst` is the next rank's landing buffer
+ * through its peer mapping), then store first_value + i in `dst_flag` (the next rank's "chunks landed" word).
+ * Everything is enqueued on `cuda_stream` in one call. */
+MAIZE_API maize_status_t maize_chain_forward(maize_ctx_t *ctx, const void *wait_flag, uint32_t first_value, void *dst,
+                                             const void *src, uint64_t total_bytes, uint64_t chunk_bytes,
+                                             void *dst_flag, void *cuda_stream);
 MAIZE_API maize_status_t maize_flags_wait(maize_ctx_t *ctx, const void *flags, uint32_t count, uint32_t value,
                                           void *cuda_stream);
 MAIZE_API maize_status_t maize_flag_store(maize_ctx_t *ctx, void *flag, uint32_t value, void *cuda_stream);

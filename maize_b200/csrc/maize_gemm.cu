@@ -953,6 +953,37 @@ maize_status_t maize_copy_async(maize_ctx_t *ctx, void *dst, const void *src, ui
     return MAIZE_OK;
 }
 
+maize_status_t maize_chain_forward(maize_ctx_t *ctx, const void *wait_flag, uint32_t first_value, void *dst,
+                                   const void *src, uint64_t total_bytes, uint64_t chunk_bytes, void *dst_flag,
+                                   void *cuda_stream)
+{
+    if (!ctx)
+        return MAIZE_ERR_INVALID_ARG;
+    if (!dst || !src || !dst_flag || chunk_bytes == 0 || reinterpret_cast<uintptr_t>(dst_flag) % 4 != 0 ||
+        reinterpret_cast<uintptr_t>(wait_flag) % 4 != 0)
+        return fail(ctx, MAIZE_ERR_INVALID_ARG, "chain: bad pointer or chunk size");
+    DeviceGuard guard(ctx->device);
+    cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+    uint32_t value = first_value;
+    for (uint64_t off = 0; off < total_bytes; off += chunk_bytes, ++value) {
+        const uint64_t nbytes = total_bytes - off < chunk_bytes ? total_bytes - off : chunk_bytes;
+        if (wait_flag) {  // forward chunk i only once it has landed here
+            maize::flags_wait_kernel<<<1, 32, 0, stream>>>(static_cast<const uint32_t *>(wait_flag), 1, value,
+                                                           ctx->d_status, ctx->timeout_ns);
+            ctx->launches += 1;
+        }
+        cudaError_t e = cudaMemcpyAsync(static_cast<char *>(dst) + off, static_cast<const char *>(src) + off, nbytes,
+                                        cudaMemcpyDeviceToDevice, stream);
+        if (e != cudaSuccess)
+            return fail_cuda(ctx, "cudaMemcpyAsync", e);
+        maize::flag_store_kernel<<<1, 32, 0, stream>>>(static_cast<uint32_t *>(dst_flag), value);
+        ctx->launches += 1;
+        if ((e = cudaGetLastError()) != cudaSuccess)
+            return fail_cuda(ctx, "kernel launch", e);
+    }
+    return MAIZE_OK;
+}
+
 maize_status_t maize_flags_wait(maize_ctx_t *ctx, const void *flags, uint32_t count, uint32_t value, void *cuda_stream)
 {
     if (!ctx)

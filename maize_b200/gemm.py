@@ -183,6 +183,12 @@ class Context:
         """Device-to-device copy on the copy engines; dst may be a peer-mapped address."""
         self._check(self._lib.maize_copy_async(self._h, dst_ptr, src_ptr, nbytes, _stream_handle(stream)))
 
+    def chain_forward(self, wait_flag_ptr, first_value: int, dst_ptr: int, src_ptr: int, total_bytes: int,
+                      chunk_bytes: int, dst_flag_ptr: int, stream=None) -> None:
+        """Enqueue (wait for chunk i, copy it to the next rank, publish i) for every chunk of a step in one call."""
+        self._check(self._lib.maize_chain_forward(self._h, wait_flag_ptr, first_value & 0xFFFFFFFF, dst_ptr, src_ptr,
+                                                  total_bytes, chunk_bytes, dst_flag_ptr, _stream_handle(stream)))
+
     def flags_wait(self, flags_ptr: int, count: int, value: int, stream=None) -> None:
         self._check(self._lib.maize_flags_wait(self._h, flags_ptr, count, value & 0xFFFFFFFF, _stream_handle(stream)))
 

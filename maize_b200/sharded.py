@@ -118,7 +118,8 @@ class NShardedGemm:
 
     def __init__(self, m: int, n: int, k: int, group=None, root: int = 0, slabs: int = 0,
                  gemm_fn: Optional[Callable] = None, device=None, ctx=None, transport: str = "auto",
-                 push_ctas: int = 0, mc_stages: int = 1, **plan_args):
+                 push_ctas: int = 0, mc_stages: int = 1, chain_rows: int = 1024,
+                 chain_in_library: bool = False, **plan_args):
         import torch
         import torch.distributed as dist
         self.dist = dist
@@ -146,6 +147,8 @@ class NShardedGemm:
         self.gemm_fn = gemm_fn
         self._a_local = None
         self.push_ctas = push_ctas
+        self.chain_rows = max(256, chain_rows // 256 * 256)  # rows of A per forwarded chunk
+        self.chain_in_library = chain_in_library  # enqueue a step's forwarding with one library call
         self.mc_stages = mc_stages  # 2: root scatters chunks, every rank multicasts its own; 1: the root multicasts everything
         self.step = 0
         self.transport = "nccl"
@@ -270,8 +273,6 @@ class NShardedGemm:
         self.step += 1
         return c_shard
 
-    _CHAIN_ROWS = 1024  # rows of A per forwarded chunk
-
     def _run_chain(self, a_root, b_shard, c_shard):
         """Rank r receives chunks from r - 1 and forwards them to r + 1 with copy-engine copies; the flag word
         LANDED of a rank counts the chunks that have arrived there.  Ranks are chained in rank order from the root
@@ -280,7 +281,7 @@ class NShardedGemm:
         mc, ctx, G = self._mc, self.ctx, self.world
         if self.root != 0:
             raise RuntimeError("the chain transport expects the root to be rank 0")
-        chunks = slab_bounds(self.m, -(-self.m // self._CHAIN_ROWS), align=256)
+        chunks = [(lo, min(self.m, lo + self.chain_rows)) for lo in range(0, self.m, self.chain_rows)]
         C = len(chunks)
         parity = self.step & 1
         base = self.step * C
@@ -298,7 +299,11 @@ class NShardedGemm:
                 # the next rank's buffer of this parity was last used in step - 2
                 ctx.flags_wait(flags_local + self._W_ACK * 4, 1, self.step - 1, stream=push)
             src_base = a_root.data_ptr() if r == 0 else mc["local_base"] + par_off
-            for i, (lo, hi) in enumerate(chunks):
+            if self.chain_in_library:
+                ctx.chain_forward(None if r == 0 else flags_local + self._W_LANDED * 4, base + 1, nxt + par_off, src_base,
+                                  self.m * row_bytes, self.chain_rows * row_bytes,
+                                  nxt + mc["flags_off"] + self._W_LANDED * 4, stream=push)
+            for i, (lo, hi) in enumerate(chunks if not self.chain_in_library else []):
                 if r != 0:
                     ctx.flags_wait(flags_local + self._W_LANDED * 4, 1, base + i + 1, stream=push)
                 ctx.copy_async(nxt + par_off + lo * row_bytes, src_base + lo * row_bytes, (hi - lo) * row_bytes,

@@ -16,7 +16,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, transport, m, n, k, steps, out_dir):
+def _worker(rank, world, port, transport, m, n, k, steps, out_dir, extra=None):
     import torch
     import torch.distributed as dist
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_DEBUG="WARN")
@@ -28,7 +28,7 @@ def _worker(rank, world, port, transport, m, n, k, steps, out_dir):
         from maize_b200.sharded import NShardedGemm
         from oracle import oracle
         ctx = maize_b200.Context(rank)
-        op = NShardedGemm(m, n, k, ctx=ctx, device=dev, transport=transport, slabs=3)
+        op = NShardedGemm(m, n, k, ctx=ctx, device=dev, transport=transport, slabs=3, **(extra or {}))
         assert op.transport == transport
         b_full = oracle.fill_bf16(31, 1, (n, k))
         b_shard = torch.from_numpy(b_full[op.lo:op.hi].view(np.int16)).to(dev).view(torch.bfloat16)
@@ -65,3 +65,23 @@ def test_two_gpu_sharded_gemm(tmp_path, oracle, transport):
         ref = oracle.gemm_bf16(a, b)
         got = np.concatenate([np.load(tmp_path / f"c_{step}_{r}.npy") for r in range(world)], axis=1)
         assert_parity(oracle, got, ref, k, oracle.max_abs_bf16(a), oracle.max_abs_bf16(b), f"{transport} step {step}")
+
+
+def test_chain_enqueued_by_the_library(tmp_path, oracle):
+    """The chain transport with the whole step's forwarding enqueued by one library call and small chunks; uses as
+    many GPUs as the box has (up to 4), so that middle ranks (receive and forward) are covered when there are > 2."""
+    import torch
+    import torch.multiprocessing as mp
+    world = min(torch.cuda.device_count(), 4)
+    if world < 2:
+        pytest.skip("needs two GPUs")
+    from helpers import assert_parity
+    m, n, k, steps = 1500, 1300, 520, 5
+    extra = dict(chain_rows=256, chain_in_library=True)
+    mp.spawn(_worker, args=(world, _free_port(), "chain", m, n, k, steps, str(tmp_path), extra), nprocs=world, join=True)
+    b = oracle.fill_bf16(31, 1, (n, k))
+    for step in range(steps):
+        a = oracle.fill_bf16(100 + step, 0, (m, k))
+        ref = oracle.gemm_bf16(a, b)
+        got = np.concatenate([np.load(tmp_path / f"c_{step}_{r}.npy") for r in range(world)], axis=1)
+        assert_parity(oracle, got, ref, k, oracle.max_abs_bf16(a), oracle.max_abs_bf16(b), f"chain in library, step {step}")
