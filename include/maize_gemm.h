@@ -214,6 +214,19 @@ MAIZE_API maize_status_t maize_scatter_push(maize_ctx_t *ctx, const void *src, v
  * NVLink without any SM taking part).  Building block of the "chain" transport of the N-sharded path. */
 MAIZE_API maize_status_t maize_copy_async(maize_ctx_t *ctx, void *dst, const void *src, uint64_t bytes,
                                           void *cuda_stream);
+/* C = A * B^T like maize_gemm_bf16_ld, for an A whose rows are still arriving IN ROW ORDER while the kernel runs
+ * (the receiving ranks of the N-sharded multi-GPU path: one launch per step instead of one per row slab).
+ * Whoever delivers A counts chunks of `rows_per_count` rows in the 32-bit word `rows_landed` (this GPU's memory, a
+ * peer-mapped address or mapped host memory), storing it with release semantics after the chunk's bytes: rows
+ * [0, r) of A are read only once (int32)(*rows_landed - landed_base) >= ceil(r / rows_per_count).  Tiles are visited
+ * in ascending groups of rows (see "group_rows"), each CTA's loader waits for its tile's rows, and the wait is
+ * bounded like every other: if the count does not arrive within "timeout_ns" the kernel ends and
+ * maize_ctx_poll returns MAIZE_ERR_TIMEOUT (C is then incomplete).  Decode-shaped problems run on the tiled
+ * kernels here.  No reference counterpart (the reference is single-GPU, crates/maize_tile/src/gemm.rs:110). */
+MAIZE_API maize_status_t maize_gemm_bf16_gated(maize_ctx_t *ctx, const void *a, uint64_t lda, const void *b,
+                                               uint64_t ldb, void *c, uint64_t ldc, uint32_t m, uint32_t n, uint32_t k,
+                                               const void *rows_landed, uint32_t landed_base, uint32_t rows_per_count,
+                                               void *cuda_stream);
 /* One step of a rank's part in the chain: cut `total_bytes` at `src` into chunks of `chunk_bytes`; for chunk i
  * (i = 0, 1, ...) wait (bounded, if `wait_flag` is not NULL) until the local word `wait_flag` has reached
  * first_value + i, copy the chunk to `dst` + its offset (copy engines; `dst` is the next rank's landing buffer

@@ -54,6 +54,7 @@ SYMBOLS = {
     "maize_mc_push_after": (_int, [_vp, _vp, _u32, _vp, _vp, _u64, _vp, _u32, _int, _vp]),
     "maize_scatter_push": (_int, [_vp, _vp, ctypes.POINTER(_vp), ctypes.POINTER(_vp), _u32, _u32, _u64, _u32, _int, _vp]),
     "maize_copy_async": (_int, [_vp, _vp, _vp, _u64, _vp]),
+    "maize_gemm_bf16_gated": (_int, [_vp, _vp, _u64, _vp, _u64, _vp, _u64, _u32, _u32, _u32, _vp, _u32, _u32, _vp]),
     "maize_chain_forward": (_int, [_vp, _vp, _u32, _vp, _vp, _u64, _u64, _vp, _vp]),
     "maize_flags_wait": (_int, [_vp, _vp, _u32, _u32, _vp]),
     "maize_flag_store": (_int, [_vp, _vp, _u32, _vp]),

@@ -106,7 +106,51 @@ struct GemmParams {
     //   bit 0: every load fetches tile (0, 0), so all operand traffic hits in L2;
     //   bit 1: no loads at all, the producer only signals "full" (upper bound of the MMA issue path).
     uint32_t debug_flags;
+    // Optional gate on the rows of A (null in normal use).  A may still be arriving, in order of its rows, while
+    // the kernel runs: whoever delivers it counts chunks of `gate_rows` rows in the 32-bit word `*gate`, and rows
+    // [0, r) may be read once the word has reached gate_base + ceil(r / gate_rows).  The producer of a CTA waits
+    // (bounded) for the rows of its tile before the tile's first load; the word may live in this GPU's memory,
+    // a peer's or in mapped host memory.
+    const uint32_t *gate = nullptr;
+    uint32_t gate_base = 0;
+    uint32_t gate_rows = 1;
 };
+
+__device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t *p)
+{
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// Producer-side wait for rows [0, row_end) of a gated A.  `seen` caches the chunk count read last, so that a
+// tile whose rows are known to have landed costs no load.  Role 5 in the status word = this wait gave up.
+__device__ __forceinline__ bool gate_rows_landed(const GemmParams &p, uint32_t row_end, int32_t &seen, const WaitCtl &ctl)
+{
+    if (p.gate == nullptr)
+        return true;
+    const int32_t need = static_cast<int32_t>((min(row_end, p.m) + p.gate_rows - 1) / p.gate_rows);
+    if (seen >= need)
+        return true;
+    const uint64_t t0 = ptx::global_timer_ns();
+    for (uint32_t it = 0;; ++it) {
+        seen = static_cast<int32_t>(ld_acquire_sys_u32(p.gate) - p.gate_base);  // wrap-around safe
+        if (seen >= need)
+            break;
+        if ((it & 15u) == 15u) {
+            if (*ctl.abort_flag)
+                return false;
+            if (ptx::global_timer_ns() - t0 > ctl.budget_ns) {
+                record_timeout(ctl, 5);
+                return false;
+            }
+        }
+        __nanosleep(200);
+    }
+    // the tile loads that follow go through the async proxy: order them after the acquire above
+    asm volatile("fence.proxy.async.global;" ::: "memory");
+    return true;
+}
 
 // Slots of the per-CTA profile: cycles a role spent blocked in its waits, and the CTA's lifetime.
 enum ProfileSlot {

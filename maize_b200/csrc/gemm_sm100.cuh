@@ -116,11 +116,14 @@ gemm_bf16_sm100_1cta(const __grid_constant__ CUtensorMap tma_a, const __grid_con
             uint32_t stage = 0, phase = 0;
             bool ok = true;
             unsigned long long w_empty = 0;
+            int32_t gate_seen = 0;
             for (uint32_t t = blockIdx.x; ok && t < num_tiles; t += gridDim.x) {
                 const TileCoord tc = tile_coord(t, p.tiles_m, p.tiles_n, p.group_m);
                 const bool hot = (p.debug_flags & 1u) != 0u;
                 const int32_t m0 = hot ? 0 : static_cast<int32_t>(tc.m_blk * kBlockM);
                 const int32_t n0 = hot ? 0 : static_cast<int32_t>(tc.n_blk * BN);
+                if (!(ok = gate_rows_landed(p, static_cast<uint32_t>(m0) + kBlockM, gate_seen, ctl)))
+                    break;
                 for (uint32_t kb = 0; kb < num_kb; ++kb) {
                     WaitTimer wt(prof);
                     ok = wait_bounded(empty_bar(stage), phase ^ 1u, ctl, 1);

@@ -119,6 +119,7 @@ gemm_bf16_sm100_2cta(const __grid_constant__ CUtensorMap tma_a, const __grid_con
             uint32_t stage = 0, phase = 0;
             bool ok = true;
             unsigned long long w_empty = 0;
+            int32_t gate_seen = 0;
             // L2 policy: the row panel of A is re-read by every column block of the sweep, B passes once
             const bool hints = (p.debug_flags & 4u) != 0u;
             const uint64_t pol_a = hints ? ptx::policy_evict_last() : ptx::policy_evict_normal();
@@ -128,6 +129,8 @@ gemm_bf16_sm100_2cta(const __grid_constant__ CUtensorMap tma_a, const __grid_con
                 const bool hot = (p.debug_flags & 1u) != 0u;
                 const int32_t m0 = static_cast<int32_t>((hot ? 0 : tc.m_blk * kPairBlockM) + cta_rank * kBlockM);
                 const int32_t n0 = static_cast<int32_t>((hot ? 0 : tc.n_blk * BN) + cta_rank * (BN / 2));
+                if (!(ok = gate_rows_landed(p, static_cast<uint32_t>(m0) + kBlockM, gate_seen, ctl)))
+                    break;
                 for (uint32_t step = 0; step < num_steps; ++step) {
                     WaitTimer wt(prof);
                     ok = wait_bounded<true>(empty_bar(stage), phase ^ 1u, ctl, 1);

@@ -272,9 +272,17 @@ maize_status_t launch_skinny(maize_ctx_t *ctx, int vi, const CUtensorMap &tx, co
     return MAIZE_OK;
 }
 
+// Rows of A that are still arriving while the kernel runs (maize_gemm_bf16_gated).
+struct RowGate {
+    const uint32_t *word;
+    uint32_t base;
+    uint32_t rows;
+};
+
 // b_kn: B is K x N row-major with row pitch ldb (C = A * B) instead of N x K (C = A * B^T).
 maize_status_t gemm_impl(maize_ctx_t *ctx, const void *a, uint64_t lda, const void *b, uint64_t ldb, void *c,
-                         uint64_t ldc, uint32_t m, uint32_t n, uint32_t k, cudaStream_t stream, bool b_kn = false)
+                         uint64_t ldc, uint32_t m, uint32_t n, uint32_t k, cudaStream_t stream, bool b_kn = false,
+                         const RowGate *gate = nullptr)
 {
     if (!ctx)
         return MAIZE_ERR_INVALID_ARG;
@@ -305,6 +313,11 @@ maize_status_t gemm_impl(maize_ctx_t *ctx, const void *a, uint64_t lda, const vo
         return fail(ctx, MAIZE_ERR_UNSUPPORTED, "row pitch beyond the TMA limit of 2^40 bytes");
 
     int vi = pick_variant(ctx, m, n, k);
+    if (gate) {
+        // only the tiled kernels watch the gate; a forced or chosen decode kernel is replaced
+        if (vi >= kFirstSkinny)
+            vi = n > 128 ? 0 : (n > 64 ? 1 : (n > 32 ? 2 : 3));
+    }
     if (b_kn) {
         // K x N tiles come in 64-column chunks: the pair kernel or the one-CTA kernels of width >= 64
         if (ctx->force_kernel != 0) {
@@ -441,6 +454,11 @@ maize_status_t gemm_impl(maize_ctx_t *ctx, const void *a, uint64_t lda, const vo
     p.timeout_ns = ctx->timeout_ns;
     p.profile = ctx->d_profile;
     p.debug_flags = ctx->debug_flags;
+    if (gate) {
+        p.gate = gate->word;
+        p.gate_base = gate->base;
+        p.gate_rows = gate->rows;
+    }
     const uint64_t tiles = uint64_t(p.tiles_m) * p.tiles_n;
     if (tiles > 0x7fffffffull)
         return fail(ctx, MAIZE_ERR_UNSUPPORTED, "too many output tiles");
@@ -621,6 +639,19 @@ maize_status_t maize_gemm_bf16_ld(maize_ctx_t *ctx, const void *a, uint64_t lda,
                                   uint64_t ldc, uint32_t m, uint32_t n, uint32_t k, void *cuda_stream)
 {
     return gemm_impl(ctx, a, lda, b, ldb, c, ldc, m, n, k, static_cast<cudaStream_t>(cuda_stream));
+}
+
+maize_status_t maize_gemm_bf16_gated(maize_ctx_t *ctx, const void *a, uint64_t lda, const void *b, uint64_t ldb,
+                                     void *c, uint64_t ldc, uint32_t m, uint32_t n, uint32_t k,
+                                     const void *rows_landed, uint32_t landed_base, uint32_t rows_per_count,
+                                     void *cuda_stream)
+{
+    if (!ctx)
+        return MAIZE_ERR_INVALID_ARG;
+    if (!rows_landed || reinterpret_cast<uintptr_t>(rows_landed) % 4 != 0 || rows_per_count == 0)
+        return fail(ctx, MAIZE_ERR_INVALID_ARG, "gated GEMM: the counter must be a 4-byte aligned word and rows_per_count > 0");
+    const RowGate gate{static_cast<const uint32_t *>(rows_landed), landed_base, rows_per_count};
+    return gemm_impl(ctx, a, lda, b, ldb, c, ldc, m, n, k, static_cast<cudaStream_t>(cuda_stream), false, &gate);
 }
 
 maize_status_t maize_gemm_bf16_kn(maize_ctx_t *ctx, const void *a, uint32_t a_rows, uint32_t a_cols, const void *b,

@@ -147,6 +147,22 @@ class Context:
         self.gemm_ld(a.data_ptr(), lda, b.data_ptr(), ldb, out.data_ptr(), ldc, m, n, k, stream)
         return out
 
+    def gemm_gated(self, a, b, out, rows_landed_ptr: int, landed_base: int, rows_per_count: int, stream=None):
+        """``out = a @ b.T`` for an ``a`` whose rows are still arriving in row order: the kernel reads rows
+        [0, r) only once the 32-bit word at ``rows_landed_ptr`` has reached landed_base + ceil(r / rows_per_count).
+        The wait is bounded ("timeout_ns"); ``poll()`` reports a count that never came as a timeout."""
+        m, k = a.shape
+        n = b.shape[0]
+        if b.shape[1] != k or tuple(out.shape) != (m, n):
+            raise MaizeError(_ffi.INVALID_ARG, "gemm_gated: a is M x K, b is N x K, out is M x N")
+        lda = a.stride(0) if m > 1 else max(k, 1)
+        ldb = b.stride(0) if n > 1 else max(k, 1)
+        ldc = out.stride(0) if m > 1 else max(n, 1)
+        self._check(self._lib.maize_gemm_bf16_gated(self._h, a.data_ptr(), lda, b.data_ptr(), ldb, out.data_ptr(), ldc,
+                                                    m, n, k, rows_landed_ptr, landed_base & 0xFFFFFFFF, rows_per_count,
+                                                    _stream_handle(stream)))
+        return out
+
     PROFILE_SLOTS = ("producer_wait_empty", "mma_wait_full", "mma_wait_acc_empty", "epilogue_wait_acc_full",
                      "epilogue_drain", "cta_cycles", "tiles", "spare")
 

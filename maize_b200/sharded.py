@@ -119,7 +119,7 @@ class NShardedGemm:
     def __init__(self, m: int, n: int, k: int, group=None, root: int = 0, slabs: int = 0,
                  gemm_fn: Optional[Callable] = None, device=None, ctx=None, transport: str = "auto",
                  push_ctas: int = 0, mc_stages: int = 1, chain_rows: int = 1024,
-                 chain_in_library: bool = False, **plan_args):
+                 chain_in_library: bool = False, chain_fused: bool = False, **plan_args):
         import torch
         import torch.distributed as dist
         self.dist = dist
@@ -149,6 +149,8 @@ class NShardedGemm:
         self.push_ctas = push_ctas
         self.chain_rows = max(256, chain_rows // 256 * 256)  # rows of A per forwarded chunk
         self.chain_in_library = chain_in_library  # enqueue a step's forwarding with one library call
+        # one GEMM launch per step whose loaders wait for the rows of A inside the kernel, instead of one per slab
+        self.chain_fused = chain_fused
         self.mc_stages = mc_stages  # 2: root scatters chunks, every rank multicasts its own; 1: the root multicasts everything
         self.step = 0
         self.transport = "nccl"
@@ -310,7 +312,12 @@ class NShardedGemm:
                                stream=push)
                 ctx.flag_store(nxt + mc["flags_off"] + self._W_LANDED * 4, base + i + 1, stream=push)
         a = a_root if r == 0 else self._landing(parity)
-        for lo, hi in self.slabs:
+        if self.chain_fused:
+            if r == 0:
+                self.gemm_fn(a, b_shard, c_shard)
+            else:
+                ctx.gemm_gated(a, b_shard, c_shard, flags_local + self._W_LANDED * 4, base, self.chain_rows, stream=cur)
+        for lo, hi in (self.slabs if not self.chain_fused else []):
             if r != 0:
                 need = next(i for i, (c_lo, c_hi) in enumerate(chunks) if c_hi >= hi)  # last chunk covering the slab
                 ctx.flags_wait(flags_local + self._W_LANDED * 4, 1, base + need + 1, stream=cur)
