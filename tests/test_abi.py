@@ -115,3 +115,32 @@ def test_kernel_selection_table():
     assert pick(16, 16384, 4096) == "sm100_skinny_pair_m32_128xNx64_s4"
     assert pick(16, 300000, 64) == "sm100_skinny_m32_128x256x64_s4"  # more than one wave of pairs: stream-K
     assert pick(100, 4096, 4096) == "sm100_skinny_m128_128x256x64_s4"
+
+
+def _split_args(arglist):
+    """Top-level comma split of a parameter list (no nested parentheses in this API)."""
+    args = [a.strip() for a in arglist.split(",")]
+    return [a for a in args if a and a != "void"]
+
+
+def test_rust_binding_in_the_integration_notes_matches_the_header():
+    """The extern "C" block a maintainer of the reference would add cannot be compiled here (no Rust toolchain),
+    so its function names, argument counts and pointer/integer kinds are checked against the header as text."""
+    notes = (ROOT / "INTEGRATION.md").read_text()
+    block = re.search(r"```rust(.*?)```", notes, flags=re.S).group(1)
+    block = re.sub(r"//[^\n]*", "", block)
+    extern = re.search(r'extern "C" \{(.*?)\n\}', block, flags=re.S).group(1)
+    rust = {name: _split_args(args) for name, args in re.findall(r"pub fn (maize_[a-z0-9_]+)\((.*?)\)", extern, flags=re.S)}
+    assert len(rust) >= 8
+    header = re.sub(r"/\*.*?\*/", "", HEADER.read_text(), flags=re.S)
+    for name, rust_args in rust.items():
+        m = re.search(r"MAIZE_API[^;(]*?\b" + name + r"\s*\((.*?)\)\s*;", header, flags=re.S)
+        assert m, f"{name} is bound in the Rust block but not declared in the header"
+        c_args = _split_args(m.group(1))
+        assert len(c_args) == len(rust_args), (name, c_args, rust_args)
+        for c_arg, r_arg in zip(c_args, rust_args):
+            r_type = r_arg.split(":", 1)[1].strip()
+            assert ("*" in c_arg) == r_type.startswith("*"), (name, c_arg, r_arg)
+            if "*" not in c_arg:
+                width = {"uint32_t": "u32", "uint64_t": "u64", "int": "c_int", "int64_t": "i64"}[c_arg.split()[0]]
+                assert r_type == width, (name, c_arg, r_arg)
