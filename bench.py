@@ -55,7 +55,7 @@ def parse_args():
     p.add_argument("--slabs", type=int, default=0,
                    help="row slabs of A for the overlapped broadcast (N > 1); 0 = sizes from the makespan model")
     p.add_argument("--transport", default="auto", choices=["auto", "multimem", "chain", "nccl"],
-                   help="how A reaches the other GPUs at N > 1 (auto: NVSwitch multicast push when available)")
+                   help="how A reaches the other GPUs at N > 1 (auto: the copy-engine chain where symmetric memory is available, else nccl)")
     p.add_argument("--mc-stages", type=int, default=1, choices=[1, 2],
                    help="multimem transport: 2 = root scatters chunks and every GPU multicasts its own, 1 = root multicasts all")
     p.add_argument("--chain-rows", type=int, default=1024, help="chain transport: rows of A per forwarded chunk")
