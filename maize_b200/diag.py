@@ -3,12 +3,16 @@
     python -m maize_b200.diag roles  --shape 8192,8192,8192 --kernels 1,5,6 [--flags 0,1,2]
     python -m maize_b200.diag sweep  --shape 16384,16384,16384 --kernel 6 --group-rows 2048,3072,4096 --flags 0,4,12
     python -m maize_b200.diag launch --shape 16,256,64 [--kernel 7] [--flags 2] [--reps 3]
+    python -m maize_b200.diag pitch  --shape 4111,3967,4104 [--pad 56,1] [--reps 24]
 
 ``roles``  prints, per kernel variant and diagnostic flag, the time, the busiest CTA's cycle count, the
            effective SM clock and the share of its life each role spent blocked (the library's own cycle
            counters, ``maize_ctx_set("profile", 1)``).
 ``sweep``  launches one GEMM per (group_rows, debug_flags) pair, for capture under ``ncu --metrics ...``.
 ``launch`` launches one shape a few times, for ``ncu --metrics gpu__time_duration.sum``.
+``pitch``  times one shape with the operand pitch (lda = ldb) and the C pitch (ldc) as given and padded by
+           ``--pad`` elements, in the four combinations: tells a slow epilogue (C rows that are not 16-byte
+           aligned) from slow loads (operand rows whose pitch is not a multiple of 128 bytes).
 
 Diagnostic flags (``maize_ctx_set("debug_flags", f)``; results are WRONG when set): 1 = every load fetches
 tile (0, 0) so all operand traffic hits in L2, 2 = no loads at all, 4 = A loaded with an evict-last L2 hint,
@@ -30,13 +34,14 @@ def main():
     import maize_b200
 
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("mode", choices=["roles", "sweep", "launch"])
+    ap.add_argument("mode", choices=["roles", "sweep", "launch", "pitch"])
     ap.add_argument("--shape", default="8192,8192,8192", help="M,N,K")
     ap.add_argument("--kernels", default="1,5,6")
     ap.add_argument("--kernel", type=int, default=0)
     ap.add_argument("--flags", default="0")
     ap.add_argument("--group-rows", default="2048")
     ap.add_argument("--reps", type=int, default=5)
+    ap.add_argument("--pad", default="56,1", help="pitch mode: elements added to lda = ldb and to ldc")
     args = ap.parse_args()
 
     m, n, k = _ints(args.shape)
@@ -86,6 +91,29 @@ def main():
                     "producer_wait_stage": share(prof, "producer_wait_empty"),
                     "epilogue_wait_accumulator": share(prof, "epilogue_wait_acc_full"),
                     "epilogue_drain": share(prof, "epilogue_drain")}), flush=True)
+    elif args.mode == "pitch":
+        pad_ab, pad_c = _ints(args.pad)
+        sets = 4  # rotate over independent operands so that a set has left L2 before it is used again
+        for dab, dc in ((0, 0), (0, pad_c), (pad_ab, 0), (pad_ab, pad_c)):
+            lda, ldc = k + dab, n + dc
+            ops = [(torch.randn(m, lda, device="cuda").bfloat16(), torch.randn(n, lda, device="cuda").bfloat16(),
+                    torch.empty(m, ldc, device="cuda", dtype=torch.bfloat16)) for _ in range(sets)]
+
+            def run(reps):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for i in range(reps):
+                    x, w, y = ops[i % sets]
+                    ctx.gemm(x[:, :k], w[:, :k], out=y[:, :n])
+                e1.record()
+                torch.cuda.synchronize()
+                return e0.elapsed_time(e1) / reps
+
+            run(4)
+            ms = run(args.reps)
+            print(json.dumps({"lda=ldb": lda, "ldc": ldc, "ms": round(ms, 4),
+                              "tflops": round(2.0 * m * n * k / ms / 1e9, 1)}), flush=True)
+            del ops
     elif args.mode == "sweep":
         ctx.set("force_kernel", args.kernel)
         for g in _ints(args.group_rows):
