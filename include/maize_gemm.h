@@ -161,6 +161,7 @@ MAIZE_API maize_status_t maize_ctx_poll(maize_ctx_t *ctx, void *cuda_stream);
  * "pdl" the kernel then fetches its first B tiles before waiting for that earlier work), "debug_flags"
  * (performance diagnostics that make results WRONG: 1 = all loads hit one tile, 2 = no loads). */
 MAIZE_API maize_status_t maize_ctx_set(maize_ctx_t *ctx, const char *key, int64_t value);
+/* Reads back any key of maize_ctx_set, plus "sm_count" and "device". */
 MAIZE_API maize_status_t maize_ctx_get(const maize_ctx_t *ctx, const char *key, int64_t *value);
 
 /* Name of kernel variant `id` (1-based), NULL past the end; id of the variant the

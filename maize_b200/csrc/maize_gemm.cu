@@ -864,6 +864,18 @@ maize_status_t maize_ctx_get(const maize_ctx_t *ctx, const char *key, int64_t *v
         *value = ctx->sm_count;
     else if (!strcmp(key, "device"))
         *value = ctx->device;
+    else if (!strcmp(key, "group_rows"))
+        *value = ctx->group_rows;
+    else if (!strcmp(key, "pdl"))
+        *value = ctx->pdl;
+    else if (!strcmp(key, "b_static"))
+        *value = ctx->b_static;
+    else if (!strcmp(key, "push_threads"))
+        *value = ctx->push_threads;
+    else if (!strcmp(key, "debug_flags"))
+        *value = ctx->debug_flags;
+    else if (!strcmp(key, "profile"))
+        *value = ctx->d_profile ? 1 : 0;
     else
         return MAIZE_ERR_INVALID_ARG;
     return MAIZE_OK;

@@ -34,6 +34,19 @@ def test_bounded_wait_returns_timeout(ctx):
     ctx.poll()  # the status word was cleared
 
 
+def test_settings_read_back(ctx):
+    """Every key of maize_ctx_set can be read with maize_ctx_get (no kernel is launched here)."""
+    for key, value in (("group_rows", 1024), ("pdl", 1), ("b_static", 1), ("push_threads", 256), ("max_ctas", 100),
+                       ("force_kernel", 2), ("debug_flags", 0)):
+        before = ctx.get(key)
+        try:
+            ctx.set(key, value)
+            assert ctx.get(key) == value, key
+        finally:
+            ctx.set(key, before)
+    assert ctx.get("sm_count") > 0 and ctx.get("device") == 0 and ctx.get("profile") == 0
+
+
 @pytest.mark.parametrize("force", [1, 2, 3, 4, 5, 6])
 def test_single_tile_single_kblock(ctx, oracle, force):
     run_case(ctx, oracle, 128, 256, 64, seed=10, force=force)
