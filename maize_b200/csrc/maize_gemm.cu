@@ -16,6 +16,7 @@
 
 #include "gemm_sm100.cuh"
 #include "gemm_sm100_2cta.cuh"
+#include "gemm_sm100_2cta_tail.cuh"
 #include "gemm_sm100_skinny.cuh"
 #include "gemm_sm100_skinny_pair.cuh"
 #include "mc_bcast.cuh"
@@ -50,11 +51,14 @@ const KernelVariant kVariants[] = {
     {"sm100_skinny_m128_128x256x64_s4", 128, 256, 256, 1},
     // K split over a CTA pair, halves added through distributed shared memory; tile width chosen per shape
     {"sm100_skinny_pair_m32_128xNx64_s4", 32, 256, 256, 2},
+    // the CTA-pair kernel with the last, partial round of tiles split along K (forced only for now)
+    {"sm100_2cta_256x256x128_s3_tail", 256, 256, 128, 2},
 };
 constexpr int kPairWide = 5;     // index of the CTA-pair kernel with 128-wide stages
 constexpr int kFirstSkinny = 6;  // indices of the skinny variants
 constexpr int kLastSkinny = 7;
 constexpr int kSkinnyPair = 8;
+constexpr int kPairTail = 9;
 constexpr int kNumVariants = static_cast<int>(sizeof(kVariants) / sizeof(kVariants[0]));
 constexpr int kMaxProfileCtas = 1024;
 constexpr int kMaxHostSlabs = 16;  // row slabs of A / C that the host entry point pipelines over PCIe
@@ -474,6 +478,48 @@ maize_status_t gemm_impl(maize_ctx_t *ctx, const void *a, uint64_t lda, const vo
         cudaMemsetAsync(ctx->d_profile, 0, sizeof(unsigned long long) * maize::kProfileSlots * kMaxProfileCtas, stream);
     }
 
+    if (vi == kPairTail) {
+        if (b_kn || gate)
+            return fail(ctx, MAIZE_ERR_UNSUPPORTED, "the tail-split kernel takes neither a K x N matrix B nor a row gate");
+        // P pairs run full_rounds rounds of whole tiles; the remaining tiles are cut into `split` k-ranges each,
+        // as many as there are idle pairs, but never fewer than 8 k-steps of 128 per part
+        const uint32_t pairs = cap;  // all pairs, also when there are fewer tiles than pairs: those get split too
+        const uint32_t steps = (k + 127) / 128;
+        maize::TailParams tp;
+        tp.g = p;
+        tp.full_rounds = static_cast<uint32_t>(tiles / pairs);
+        tp.tail_tiles = static_cast<uint32_t>(tiles % pairs);
+        tp.split = 1;
+        if (tp.tail_tiles > 0) {
+            uint32_t s = pairs / tp.tail_tiles;
+            if (s > 8)
+                s = 8;
+            if (s > steps / 8)
+                s = steps / 8;
+            const size_t slot_bytes = size_t(maize::kTailSlotFloats) * sizeof(float) * 2;  // both CTAs of a pair
+            while (s > 1 && size_t(tp.tail_tiles) * s * slot_bytes > kPartialsBytes)
+                --s;
+            if (s > 1 && tp.tail_tiles * 8u <= 4u * kMaxSkinnyTiles)
+                tp.split = s;
+        }
+        tp.partials = ctx->d_partials;
+        tp.counters = ctx->d_counters;
+        auto kernel = maize::gemm_bf16_sm100_2cta_tail<2, 3>;
+        const uint32_t smem = maize::PairSmemLayout<256, 2, 3>::kDynamicBytes;
+        if (!ctx->attr_set[vi]) {
+            cudaError_t ea = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+            if (ea != cudaSuccess)
+                return fail_cuda(ctx, "cudaFuncSetAttribute(max dynamic smem)", ea);
+            ctx->attr_set[vi] = true;
+        }
+        const uint64_t busy = tp.full_rounds > 0 ? pairs : uint64_t(tp.tail_tiles) * tp.split;
+        kernel<<<static_cast<uint32_t>(2 * busy), maize::kNumThreads, smem, stream>>>(ta, tb, tp);
+        cudaError_t el = cudaGetLastError();
+        if (el != cudaSuccess)
+            return fail_cuda(ctx, "kernel launch", el);
+        ctx->launches += 1;
+        return MAIZE_OK;
+    }
     if (b_kn) {
         switch (vi) {
         case 0: return launch_variant<256, 4, true>(ctx, vi, ta, tb, p, grid, stream);
