@@ -1106,19 +1106,24 @@ maize_status_t maize_chain_forward(maize_ctx_t *ctx, const void *wait_flag, uint
         return fail(ctx, MAIZE_ERR_INVALID_ARG, "chain: bad pointer or chunk size");
     DeviceGuard guard(ctx->device);
     cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+    // Per chunk: one copy and ONE one-thread kernel that publishes the chunk just copied and, on a rank that
+    // receives, waits for the next chunk to forward (the first chunk's wait is a launch of its own).
+    const uint32_t *wait = static_cast<const uint32_t *>(wait_flag);
+    uint32_t *publish = static_cast<uint32_t *>(dst_flag);
     uint32_t value = first_value;
+    if (wait && total_bytes > 0) {
+        maize::chain_step_kernel<<<1, 32, 0, stream>>>(nullptr, 0, wait, value, ctx->d_status, ctx->timeout_ns);
+        ctx->launches += 1;
+    }
     for (uint64_t off = 0; off < total_bytes; off += chunk_bytes, ++value) {
         const uint64_t nbytes = total_bytes - off < chunk_bytes ? total_bytes - off : chunk_bytes;
-        if (wait_flag) {  // forward chunk i only once it has landed here
-            maize::flags_wait_kernel<<<1, 32, 0, stream>>>(static_cast<const uint32_t *>(wait_flag), 1, value,
-                                                           ctx->d_status, ctx->timeout_ns);
-            ctx->launches += 1;
-        }
+        const bool more = off + chunk_bytes < total_bytes;
         cudaError_t e = cudaMemcpyAsync(static_cast<char *>(dst) + off, static_cast<const char *>(src) + off, nbytes,
                                         cudaMemcpyDeviceToDevice, stream);
         if (e != cudaSuccess)
             return fail_cuda(ctx, "cudaMemcpyAsync", e);
-        maize::flag_store_kernel<<<1, 32, 0, stream>>>(static_cast<uint32_t *>(dst_flag), value);
+        maize::chain_step_kernel<<<1, 32, 0, stream>>>(publish, value, (wait && more) ? wait : nullptr, value + 1,
+                                                       ctx->d_status, ctx->timeout_ns);
         ctx->launches += 1;
         if ((e = cudaGetLastError()) != cudaSuccess)
             return fail_cuda(ctx, "kernel launch", e);

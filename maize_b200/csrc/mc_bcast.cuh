@@ -194,4 +194,21 @@ __global__ void flag_store_kernel(uint32_t *flag, uint32_t value)
     }
 }
 
+// One step of a rank's forwarding in the chain, as ONE launch between two copies: publish `store_value` in
+// `store_flag` (the next rank's count of landed chunks; everything this stream did before, i.e. the copy of that
+// chunk, is visible first), then wait (bounded) until this rank's own count `wait_flag` has reached `wait_value`
+// (the next chunk to forward has landed here).  Either half is skipped when its pointer is null.
+__global__ void chain_step_kernel(uint32_t *store_flag, uint32_t store_value, const uint32_t *wait_flag,
+                                  uint32_t wait_value, DeviceStatus *status, uint64_t budget_ns)
+{
+    if (threadIdx.x != 0)
+        return;
+    if (store_flag) {
+        __threadfence_system();
+        st_release_sys_u32(store_flag, store_value);
+    }
+    if (wait_flag)
+        (void)flag_wait_bounded(wait_flag, wait_value, status, budget_ns, 8);
+}
+
 }  // namespace maize
