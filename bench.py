@@ -61,6 +61,8 @@ def parse_args():
     p.add_argument("--chain-rows", type=int, default=1024, help="chain transport: rows of A per forwarded chunk")
     p.add_argument("--chain-in-library", action="store_true",
                    help="chain transport: enqueue a step's forwarding with one library call instead of per-chunk calls")
+    p.add_argument("--chain-streams", type=int, default=1, choices=[1, 2],
+                   help="chain transport with --chain-in-library: streams the forwarded chunks alternate between")
     p.add_argument("--chain-fused", action="store_true",
                    help="chain transport: one gated GEMM launch per step (waits for rows inside the kernel)")
     p.add_argument("--push-ctas", type=int, default=0, help="CTAs of the multicast push kernel (0 = library default)")

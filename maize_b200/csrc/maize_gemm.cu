@@ -99,6 +99,9 @@ struct maize_ctx {
     uint32_t pdl = 0;       // launch the decode kernel with programmatic stream serialization
     uint32_t b_static = 0;  // the caller guarantees that nothing earlier in the stream writes B (weights)
     uint32_t push_threads = 512;  // threads per CTA of the copy kernels of the multi-GPU path
+    uint32_t chain_streams = 1;   // 2: maize_chain_forward alternates chunks between the caller's stream and a helper
+    cudaStream_t chain_helper = nullptr;
+    cudaEvent_t chain_ev[3] = {};  // [0], [1]: "chunk published" per stream; [2]: fork / join
     uint64_t launches = 0;
     EncodeTiledFn encode = nullptr;
     void *staging = nullptr;  // device staging for the *_host entry point
@@ -666,6 +669,11 @@ void maize_ctx_destroy(maize_ctx_t *ctx)
         cudaFree(ctx->staging);
     if (ctx->repack)
         cudaFree(ctx->repack);
+    if (ctx->chain_helper)
+        cudaStreamDestroy(ctx->chain_helper);
+    for (cudaEvent_t ev : ctx->chain_ev)
+        if (ev)
+            cudaEventDestroy(ev);
     if (ctx->copy_in)
         cudaStreamDestroy(ctx->copy_in);
     if (ctx->copy_out)
@@ -933,6 +941,10 @@ maize_status_t maize_ctx_set(maize_ctx_t *ctx, const char *key, int64_t value)
         ctx->pdl = value ? 1u : 0u;
     } else if (!strcmp(key, "b_static")) {
         ctx->b_static = value ? 1u : 0u;
+    } else if (!strcmp(key, "chain_streams")) {
+        if (value != 1 && value != 2)
+            return fail(ctx, MAIZE_ERR_INVALID_ARG, "chain_streams: 1 or 2");
+        ctx->chain_streams = static_cast<uint32_t>(value);
     } else if (!strcmp(key, "push_threads")) {
         if (value < 32 || value > 512 || value % 32 != 0)
             return fail(ctx, MAIZE_ERR_INVALID_ARG, "push_threads: a multiple of 32 in [32, 512]");
@@ -1106,6 +1118,51 @@ maize_status_t maize_chain_forward(maize_ctx_t *ctx, const void *wait_flag, uint
         return fail(ctx, MAIZE_ERR_INVALID_ARG, "chain: bad pointer or chunk size");
     DeviceGuard guard(ctx->device);
     cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+    if (ctx->chain_streams == 2 && total_bytes > chunk_bytes) {
+        // Chunks alternate between the caller's stream and a helper stream, so that the small kernels around one
+        // chunk's copy run while the other stream's copy keeps the link busy.  Counts are still published in chunk
+        // order: the publishing kernel of chunk i waits (stream event) for the one of chunk i - 1.
+        if (!ctx->chain_helper) {
+            bool ok = cudaStreamCreateWithFlags(&ctx->chain_helper, cudaStreamNonBlocking) == cudaSuccess;
+            for (int i = 0; ok && i < 3; ++i)
+                ok = cudaEventCreateWithFlags(&ctx->chain_ev[i], cudaEventDisableTiming) == cudaSuccess;
+            if (!ok)
+                return fail_cuda(ctx, "creating the chain's helper stream / events", cudaGetLastError());
+        }
+        cudaStream_t lanes[2] = {stream, ctx->chain_helper};
+        cudaError_t e;
+        // fork: the helper starts after whatever the caller queued on its stream before this call
+        if ((e = cudaEventRecord(ctx->chain_ev[2], stream)) != cudaSuccess ||
+            (e = cudaStreamWaitEvent(ctx->chain_helper, ctx->chain_ev[2], 0)) != cudaSuccess)
+            return fail_cuda(ctx, "forking the chain's helper stream", e);
+        uint32_t v = first_value;
+        uint32_t i = 0;
+        for (uint64_t off = 0; off < total_bytes; off += chunk_bytes, ++v, ++i) {
+            const uint64_t nbytes = total_bytes - off < chunk_bytes ? total_bytes - off : chunk_bytes;
+            cudaStream_t s = lanes[i & 1u];
+            if (wait_flag) {
+                maize::chain_step_kernel<<<1, 32, 0, s>>>(nullptr, 0, static_cast<const uint32_t *>(wait_flag), v,
+                                                          ctx->d_status, ctx->timeout_ns);
+                ctx->launches += 1;
+            }
+            if ((e = cudaMemcpyAsync(static_cast<char *>(dst) + off, static_cast<const char *>(src) + off, nbytes,
+                                     cudaMemcpyDeviceToDevice, s)) != cudaSuccess)
+                return fail_cuda(ctx, "cudaMemcpyAsync", e);
+            if (i > 0 && (e = cudaStreamWaitEvent(s, ctx->chain_ev[(i - 1) & 1u], 0)) != cudaSuccess)
+                return fail_cuda(ctx, "ordering the chain's publications", e);
+            maize::chain_step_kernel<<<1, 32, 0, s>>>(static_cast<uint32_t *>(dst_flag), v, nullptr, 0, ctx->d_status,
+                                                      ctx->timeout_ns);
+            ctx->launches += 1;
+            if ((e = cudaGetLastError()) != cudaSuccess)
+                return fail_cuda(ctx, "kernel launch", e);
+            if ((e = cudaEventRecord(ctx->chain_ev[i & 1u], s)) != cudaSuccess)
+                return fail_cuda(ctx, "cudaEventRecord", e);
+        }
+        // join: the caller's stream continues after the last publication (which is after all earlier ones)
+        if (((i - 1) & 1u) == 1u && (e = cudaStreamWaitEvent(stream, ctx->chain_ev[1], 0)) != cudaSuccess)
+            return fail_cuda(ctx, "joining the chain's helper stream", e);
+        return MAIZE_OK;
+    }
     // Per chunk: one copy and ONE one-thread kernel that publishes the chunk just copied and, on a rank that
     // receives, waits for the next chunk to forward (the first chunk's wait is a launch of its own).
     const uint32_t *wait = static_cast<const uint32_t *>(wait_flag);

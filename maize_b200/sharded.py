@@ -123,7 +123,8 @@ class NShardedGemm:
     def __init__(self, m: int, n: int, k: int, group=None, root: int = 0, slabs: int = 0,
                  gemm_fn: Optional[Callable] = None, device=None, ctx=None, transport: str = "auto",
                  push_ctas: int = 0, mc_stages: int = 1, chain_rows: int = 1024,
-                 chain_in_library: bool = False, chain_fused: bool = False, **plan_args):
+                 chain_in_library: bool = False, chain_fused: bool = False, chain_streams: int = 1,
+                 **plan_args):
         import torch
         import torch.distributed as dist
         self.dist = dist
@@ -155,6 +156,8 @@ class NShardedGemm:
         self.chain_in_library = chain_in_library  # enqueue a step's forwarding with one library call
         # one GEMM launch per step whose loaders wait for the rows of A inside the kernel, instead of one per slab
         self.chain_fused = chain_fused
+        if chain_streams != 1 and self.ctx is not None:  # library-enqueued forwarding alternates chunks between two streams
+            self.ctx.set("chain_streams", chain_streams)
         self.mc_stages = mc_stages  # 2: root scatters chunks, every rank multicasts its own; 1: the root multicasts everything
         self.step = 0
         self.transport = "nccl"

@@ -67,8 +67,9 @@ def test_two_gpu_sharded_gemm(tmp_path, oracle, transport):
         assert_parity(oracle, got, ref, k, oracle.max_abs_bf16(a), oracle.max_abs_bf16(b), f"{transport} step {step}")
 
 
+@pytest.mark.parametrize("streams", [1, 2])
 @pytest.mark.parametrize("fused", [False, True])
-def test_chain_enqueued_by_the_library(tmp_path, oracle, fused):
+def test_chain_enqueued_by_the_library(tmp_path, oracle, fused, streams):
     """The chain transport with the whole step's forwarding enqueued by one library call and small chunks, with the
     GEMMs launched per slab or (fused) as one gated launch per step; uses as many GPUs as the box has (up to 4), so
     that middle ranks (receive and forward) are covered when there are > 2."""
@@ -79,7 +80,7 @@ def test_chain_enqueued_by_the_library(tmp_path, oracle, fused):
         pytest.skip("needs two GPUs")
     from helpers import assert_parity
     m, n, k, steps = 1500, 1300, 520, 5
-    extra = dict(chain_rows=256, chain_in_library=True, chain_fused=fused)
+    extra = dict(chain_rows=256, chain_in_library=True, chain_fused=fused, chain_streams=streams)
     mp.spawn(_worker, args=(world, _free_port(), "chain", m, n, k, steps, str(tmp_path), extra), nprocs=world, join=True)
     b = oracle.fill_bf16(31, 1, (n, k))
     for step in range(steps):
