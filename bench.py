@@ -4,17 +4,23 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c4] [--impl ours|reference]
 
 A step is one pass of the hot path over one batch of synthetic input: one GEMM of the
-workload's shape (at N > 1: replicate A from rank 0 slab by slab over NCCL while every rank
+workload's shape (at N > 1: A is replicated from rank 0 over NVLink while every rank
 multiplies against its own N/G rows of B).  Prints ONE JSON line on rank 0.
 
 Workloads (synthetic seeded inputs of the shapes and distributions of the baseline configs):
   c1 4096^3 | c2 4111x3967x4104 ragged | c3 16x16384x4096 decode | c4 16384^3 (default) |
   c5 8192x28672x8192 MLP up-projection | t 8192^3
+
+Beside the headline the line carries: `verified` (sampled rows of every rank's C against the CPU
+oracle, computed after the timed region; the run exits non-zero if they disagree), `roofline`,
+`cpu_baseline`, `e2e`, and at N = 1 `cublas_same_run` (torch.matmul on the same tensors, interleaved
+with this library's launches) and, on the default workload, `others` (the remaining workloads, briefly).
 """
 from __future__ import annotations
 
 import argparse
 import json
+import math
 import os
 import statistics
 import subprocess
@@ -36,12 +42,13 @@ WORKLOADS = {
     "t": (8192, 8192, 8192, 1.0, 1.0, "normal", 5, "BF16 GEMM M=N=K=8192"),
 }
 L2_BYTES = 126 * 1024 * 1024
+SPEC_TFLOPS, SPEC_HBM_GBS = 2250.0, 8000.0
 # DRAM bytes per launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum of one ncu
 # capture on a B200; the summaries with the commands are under profiles/).  None where not captured.
 NCU_TRAFFIC = {
-    "c4": 9.39e9,   # profiles/gemm_pair_16384.md
-    "t": 1.214e9,   # profiles/gemm_pair_8192.md
-    "c3": 1.393e8,  # profiles/skinny_16x16384x4096.md
+    "c4": (9.39e9, "profiles/gemm_pair_16384.md"),
+    "t": (1.214e9, "profiles/gemm_pair_8192.md"),
+    "c3": (1.393e8, "profiles/skinny_16x16384x4096.md"),
 }
 
 
@@ -53,18 +60,19 @@ def parse_args():
     p.add_argument("--workload", default="c4", choices=sorted(WORKLOADS))
     p.add_argument("--impl", default="ours", choices=["ours", "reference"])
     p.add_argument("--slabs", type=int, default=0,
-                   help="row slabs of A for the overlapped broadcast (N > 1); 0 = sizes from the makespan model")
+                   help="row slabs of A when the GEMM is launched per slab (N > 1, --chain-fused 0 or not the chain); "
+                        "0 = sizes from the makespan model")
     p.add_argument("--transport", default="auto", choices=["auto", "multimem", "chain", "nccl"],
                    help="how A reaches the other GPUs at N > 1 (auto: the copy-engine chain where symmetric memory is available, else nccl)")
     p.add_argument("--mc-stages", type=int, default=1, choices=[1, 2],
                    help="multimem transport: 2 = root scatters chunks and every GPU multicasts its own, 1 = root multicasts all")
     p.add_argument("--chain-rows", type=int, default=1024, help="chain transport: rows of A per forwarded chunk")
-    p.add_argument("--chain-in-library", action="store_true",
-                   help="chain transport: enqueue a step's forwarding with one library call instead of per-chunk calls")
-    p.add_argument("--chain-streams", type=int, default=1, choices=[1, 2],
-                   help="chain transport with --chain-in-library: streams the forwarded chunks alternate between")
-    p.add_argument("--chain-fused", action="store_true",
-                   help="chain transport: one gated GEMM launch per step (waits for rows inside the kernel)")
+    p.add_argument("--chain-streams", type=int, default=2, choices=[1, 2],
+                   help="chain transport: streams the forwarded chunks alternate between")
+    p.add_argument("--chain-fused", type=int, default=1, choices=[0, 1],
+                   help="chain transport: 1 = one gated GEMM launch per step (waits for rows inside the kernel), 0 = one per slab")
+    p.add_argument("--serial-steps", action="store_true",
+                   help="N > 1: the replication of a step waits for the previous step's GEMM on the root (no overlap across steps)")
     p.add_argument("--push-ctas", type=int, default=0, help="CTAs of the multicast push kernel (0 = library default)")
     p.add_argument("--e2e-steps", type=int, default=3)
     p.add_argument("--b-layout", default="nk", choices=["nk", "kn"],
@@ -73,7 +81,10 @@ def parse_args():
                    help="c3 only: do not use programmatic dependent launch with static weights for the decode kernel")
     p.add_argument("--no-cpu-baseline", action="store_true")
     p.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (for profiler captures)")
+    p.add_argument("--no-others", action="store_true", help="skip the brief runs of the other workloads and of cuBLAS")
+    p.add_argument("--no-verify", action="store_true", help="skip the check against the CPU oracle (for profiler captures)")
     p.add_argument("--force-kernel", type=int, default=0, help="kernel variant id (0 = the library's heuristic)")
+    p.add_argument("--repack", action="store_true", help="give the context scratch for the pitch-aligning pre-pass")
     p.add_argument("--cpu-seconds", type=float, default=10.0, help="target CPU time of the cpu_baseline sample")
     return p.parse_args()
 
@@ -92,18 +103,48 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while the timed region runs."""
+    """Samples the SM clock and the throttle reasons of one GPU while the timed regions run: NVML every 5 ms from a
+    thread of this process (read-only queries), or `nvidia-smi -lms 100` when NVML cannot be loaded."""
+    REASONS = ((0x4, "sw_power_cap"), (0x8, "hw_slowdown"), (0x20, "sw_thermal_slowdown"), (0x40, "hw_thermal_slowdown"))
     FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
               "clocks_event_reasons.sw_power_cap")
 
     def __init__(self, gpu_uuid: str):
-        self.rows = []
-        self.proc = None
+        self.rows = []  # (wall time, sm MHz, max MHz, set of active reasons)
         self.uuid = gpu_uuid
+        self.proc = None
         self.thread = None
+        self.stop_flag = False
+        self.how = None
 
     def start(self):
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            handle = pynvml.nvmlDeviceGetHandleByUUID(self.uuid)
+            mx = float(pynvml.nvmlDeviceGetMaxClockInfo(handle, pynvml.NVML_CLOCK_SM))
+            reasons_fn = getattr(pynvml, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
+                pynvml.nvmlDeviceGetCurrentClocksThrottleReasons
+            pynvml.nvmlDeviceGetClockInfo(handle, pynvml.NVML_CLOCK_SM)
+            reasons_fn(handle)
+
+            def poll():
+                while not self.stop_flag:
+                    try:
+                        sm = float(pynvml.nvmlDeviceGetClockInfo(handle, pynvml.NVML_CLOCK_SM))
+                        mask = int(reasons_fn(handle))
+                        self.rows.append((time.time(), sm, mx, {n for bit, n in self.REASONS if mask & bit}))
+                    except Exception:
+                        pass
+                    time.sleep(0.005)
+
+            self.how = "nvml, 5 ms"
+            self.thread = threading.Thread(target=poll, daemon=True)
+            self.thread.start()
+            return
+        except Exception:
+            pass
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", self.uuid, f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
@@ -111,14 +152,24 @@ class ClockSampler:
         except Exception:
             self.proc = None
             return
-        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.how = "nvidia-smi, 100 ms"
+        self.thread = threading.Thread(target=self._read_smi, daemon=True)
         self.thread.start()
 
-    def _read(self):
+    def _read_smi(self):
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for line in self.proc.stdout:
-            self.rows.append((time.time(), line.strip()))
+            parts = [x.strip() for x in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm, mx = float(parts[0]), float(parts[1])
+            except ValueError:
+                continue
+            self.rows.append((time.time(), sm, mx, {n for n, v in zip(names, parts[3:7]) if v.lower().startswith("active")}))
 
     def stop(self):
+        self.stop_flag = True
         if self.proc is not None:
             self.proc.terminate()
             try:
@@ -127,39 +178,57 @@ class ClockSampler:
                 self.proc.kill()
 
     def summary(self, t0: float, t1: float):
-        sm, mx, reasons = [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        rows = [r for r in self.rows if t0 <= r[0] <= t1 + 0.15] or self.rows[-3:]
-        for _, line in rows:
-            parts = [x.strip() for x in line.split(",")]
-            if len(parts) < 7:
-                continue
-            try:
-                sm.append(float(parts[0]))
-                mx.append(float(parts[1]))
-            except ValueError:
-                continue
-            for name, val in zip(names, parts[3:7]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
-        if not sm:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
-        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
-                "samples": len(sm)}
+        pad = 0.15 if self.proc is not None else 0.0
+        rows = [r for r in self.rows if t0 <= r[0] <= t1 + pad] or self.rows[-3:]
+        if not rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0, "how": self.how}
+        reasons = set()
+        for r in rows:
+            reasons |= r[3]
+        return {"sm_mhz": statistics.median(r[1] for r in rows), "sm_max_mhz": max(r[2] for r in rows),
+                "reasons": sorted(reasons), "samples": len(rows), "how": self.how}
+
+
+def config_for(args, world: int):
+    """The `config` object of the JSON line; a function of the command line only, so that both arms print the same."""
+    m, n, k, *_rest, desc = WORKLOADS[args.workload]
+    rank_bytes = 2 * (m * k + (n // world) * k + m * (n // world))
+    small = rank_bytes < 2 * L2_BYTES
+    n_sets = max(1, -(-4 * L2_BYTES // rank_bytes)) if small else 1
+    kn = args.b_layout == "kn"
+    transport = "chain" if args.transport == "auto" else args.transport
+    how = {"multimem": "NVSwitch multicast (multimem.st push kernel)",
+           "chain": f"a copy-engine chain (rank r forwards to r+1 in {args.chain_rows}-row chunks over {args.chain_streams} "
+                    f"stream(s); {'one gated GEMM launch per step' if args.chain_fused else 'one GEMM launch per row slab'}; "
+                    + ("replication of a step waits for the previous step's GEMM" if args.serial_steps else
+                       "A resident on the root, its readiness given by an event: the replication of step s+1 "
+                       "overlaps the math of step s, landing buffers double-buffered") + ")",
+           "nccl": "NCCL broadcast per row slab"}[transport]
+    decode_pdl = args.workload == "c3" and not args.no_pdl
+    return {
+        "workload": f"{args.workload}: {desc}", "M": m, "N": n, "K": k,
+        "layout": "A MxK row-major, B KxN row-major, C MxN bf16" if kn else "A MxK row-major, B NxK K-major, C MxN bf16",
+        "parallelism": "single GPU" if world == 1 else f"N-sharded x{world}, A replicated from rank 0 every step by " + how,
+        "l2": (f"rotating over {n_sets} independent input sets ({n_sets * rank_bytes >> 20} MiB > 4x L2), "
+               "back-to-back launches") if small else "inputs exceed L2 (back-to-back launches)",
+        "algorithmic_bytes": 2 * (m * k + n * k + m * n),
+        "launch": "programmatic dependent launch, B declared static (weights)" if decode_pdl else "plain",
+    }
 
 
 def cpu_sample(workload: str, seconds: float, steps: int = 1, warmup: int = 0):
     """Times the CPU oracle (port of the path's numeric contract; the reference has no CPU GEMM) on a
-    bounded row slab of the workload with every host thread; returns TFLOP/s and a description."""
-    import numpy as np
+    bounded row slab of the workload with every host core this process may use; returns TFLOP/s and a description."""
     from oracle import oracle
+    threads = oracle.host_cores()
+    oracle.set_num_threads(threads)  # a launcher may have exported OMP_NUM_THREADS=1
     m, n, k, sa, sb, dist, seed, _ = WORKLOADS[workload]
     d = oracle.UNIFORM if dist == "uniform" else oracle.NORMAL
     b = oracle.fill_bf16(seed, 1, (n, k), d, sb)
     probe_rows = min(m, 8)
     a = oracle.fill_bf16(seed, 0, (probe_rows, k), d, sa)
     t0 = time.perf_counter()
-    oracle.gemm_bf16(a, b)
+    oracle.gemm_bf16(a, b, nthreads=threads)
     dt = max(time.perf_counter() - t0, 1e-6)
     per_row = dt / probe_rows
     rows = int(max(8, min(m, (seconds / max(steps + warmup, 1)) / per_row)))
@@ -168,7 +237,7 @@ def cpu_sample(workload: str, seconds: float, steps: int = 1, warmup: int = 0):
     times = []
     for i in range(warmup + steps):
         t0 = time.perf_counter()
-        oracle.gemm_bf16(a, b)
+        oracle.gemm_bf16(a, b, nthreads=threads)
         dt = time.perf_counter() - t0
         if i >= warmup:
             times.append(dt)
@@ -177,7 +246,7 @@ def cpu_sample(workload: str, seconds: float, steps: int = 1, warmup: int = 0):
     return {
         "tflops": flops * len(times) / total / 1e12,
         "ms_per_step": 1e3 * total / len(times),
-        "cores": oracle.num_threads(),
+        "cores": threads,
         "rows": rows,
         "sample": f"first {rows} of {m} rows of A against all of B ({n}x{k}), full K; "
                   f"{'whole workload' if rows == m else 'rate extrapolates linearly in M'}",
@@ -190,7 +259,6 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    m, n, k, *_ = WORKLOADS[args.workload]
     r = cpu_sample(args.workload, seconds=40.0, steps=args.steps, warmup=args.warmup)
     unit = "TFLOP/s"
     line = {
@@ -198,13 +266,128 @@ def run_reference(args):
         "metric": "BF16 GEMM TFLOP/s", "value": r["tflops"], "unit": unit, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": r["ms_per_step"], "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "bf16 in, fp32 accumulate", "data": "synthetic",
-        "config": {"workload": f"{args.workload}: {WORKLOADS[args.workload][7]}", "M": m, "N": n, "K": k},
+        "config": config_for(args, args.gpus),
         "cpu_baseline": {"value": r["tflops"], "unit": unit, "cores": r["cores"], "kind": "port",
                          "sample": r["sample"]},
         "e2e": {"value": r["tflops"], "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)
+
+
+def sample_rows(m: int, count: int, seed: int, marks=()):
+    """Row indices to verify: the first and last rows, rows on both sides of every mark (chunk and slab
+    boundaries), and random ones."""
+    import numpy as np
+    picks = list(range(min(4, m))) + list(range(max(0, m - 4), m))
+    for b in marks:
+        picks += [x for x in (b - 1, b) if 0 <= x < m]
+    rng = np.random.default_rng(seed)
+    picks += [int(x) for x in rng.integers(0, m, max(count - len(picks), 8))]
+    return np.unique(np.array(picks, dtype=np.int64))
+
+
+def check_rows(a_rows, b_host, got_rows, k: int, threads: int):
+    """Sampled rows of C against the CPU oracle, with the two bounds of the parity tests: the path's tolerance
+    1e-2 * sqrt(K) * max|a| * max|b| + one bf16 ulp, and the tight bug-catching bound 1e-4 * sqrt(K) * max|a| * max|b|
+    + one bf16 ulp.  Returns (ok, max abs error, path bound)."""
+    import numpy as np
+    from oracle import oracle
+    ref = oracle.gemm_bf16(a_rows, b_host, nthreads=threads)
+    ma, mb = oracle.max_abs_bf16(a_rows), oracle.max_abs_bf16(b_host)
+    ok, err, bound, _bad = oracle.check(got_rows, ref, k, ma, mb)
+    g = oracle.bf16_to_f32(got_rows).astype(np.float64)
+    r = oracle.bf16_to_f32(ref).astype(np.float64)
+    tight = np.abs(r) * 2.0 ** -7 + 1e-4 * math.sqrt(max(k, 1)) * ma * mb
+    ok = bool(ok) and bool(np.all(np.abs(g - r) <= tight))
+    return ok, float(err), float(bound)
+
+
+def to_u16(t):
+    import numpy as np
+    import torch
+    return t.contiguous().view(torch.int16).cpu().numpy().view(np.uint16)
+
+
+def time_loop(fn, reps: int):
+    """Average milliseconds of `reps` back-to-back calls, CUDA events on the current stream, with wall-clock
+    marks for the clock sampler."""
+    import torch
+    torch.cuda.synchronize()
+    w0 = time.time()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(reps):
+        fn(i)
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / reps, w0, time.time()
+
+
+def draw(shape, sigma, dname, dev, gen):
+    import torch
+    if dname == "uniform":
+        return ((torch.rand(shape, device=dev, generator=gen) * 2 - 1) * sigma).to(torch.bfloat16)
+    return (torch.randn(shape, device=dev, generator=gen) * sigma).to(torch.bfloat16)
+
+
+def brief_workload(ctx, name: str, dev, peaks, sampler, reps: int, pdl: bool = False, cublas: bool = True):
+    """One of the other workloads on one GPU: warm up, time `reps` launches (rotating over input sets when the
+    inputs fit in L2), the same with torch.matmul, and check sampled rows against the CPU oracle."""
+    import torch
+    from oracle import oracle
+    m, n, k, sa, sb, dname, seed, desc = WORKLOADS[name]
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(7000 + seed)
+    nbytes = 2 * (m * k + n * k + m * n)
+    n_sets = max(1, -(-4 * L2_BYTES // nbytes)) if nbytes < 2 * L2_BYTES else 1
+    sets = [(draw((m, k), sa, dname, dev, gen), draw((n, k), sb, dname, dev, gen),
+             torch.empty((m, n), dtype=torch.bfloat16, device=dev)) for _ in range(n_sets)]
+    ctx.set("pdl", 1 if pdl else 0)
+    ctx.set("b_static", 1 if pdl else 0)
+    try:
+        def ours(i):
+            a, b, c = sets[i % n_sets]
+            ctx.gemm(a, b, out=c)
+        for i in range(3):
+            ours(i)
+        total = max(reps, 3) * n_sets if n_sets > 1 else max(reps, 3)
+        ms, w0, w1 = time_loop(ours, total)
+        ctx.poll()
+    finally:
+        ctx.set("pdl", 0)
+        ctx.set("b_static", 0)
+    out = {"workload": f"{name}: {desc}", "kernel": ctx.pick_kernel(m, n, k), "ms": ms,
+           "launch": "programmatic dependent launch, B declared static" if pdl else "plain",
+           "clocks": sampler.summary(w0, w1) if sampler else None}
+    if name == "c3":
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        out.update(value=gbs, unit="GB/s", roofline={"bound": "hbm", "frac": gbs / peaks["hbm_gbs"], "peak": peaks["hbm_gbs"],
+                                                     "frac_of_spec_8TBs": gbs / SPEC_HBM_GBS})
+    else:
+        tf = 2.0 * m * n * k / (ms * 1e-3) / 1e12
+        out.update(value=tf, unit="TFLOP/s", roofline={"bound": "tensor", "frac": tf / peaks["bf16_tflops"],
+                                                       "peak": peaks["bf16_tflops"], "frac_of_spec_2250": tf / SPEC_TFLOPS})
+    if cublas:
+        c2 = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
+
+        def lib(i):
+            a, b, _ = sets[i % n_sets]
+            torch.matmul(a, b.t(), out=c2)
+        for i in range(3):
+            lib(i)
+        ms_lib, _, _ = time_loop(lib, total)
+        out["cublas_ms"] = ms_lib
+        del c2
+    # sampled rows of the last launch's output against the oracle
+    a, b, c = sets[(total - 1) % n_sets]
+    rows = sample_rows(m, 16, seed)
+    idx = torch.from_numpy(rows).to(dev)
+    ok, err, bound = check_rows(to_u16(a[idx]), to_u16(b), to_u16(c[idx]), k, oracle.host_cores())
+    out["verified"] = {"rows": int(len(rows)), "max_err": err, "bound": bound, "ok": ok}
+    del sets, a, b, c
+    torch.cuda.empty_cache()
+    return out
 
 
 def main():
@@ -217,6 +400,7 @@ def main():
     import torch.distributed as dist
     import maize_b200
     from maize_b200.sharded import NShardedGemm, shard_bounds
+    from oracle import oracle
 
     # NCCL prints its version banner on stdout at VERSION level; stdout must carry the JSON line only
     if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
@@ -232,6 +416,8 @@ def main():
     dev = torch.device("cuda", local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
+    host_threads = max(1, oracle.host_cores() // world)
+    oracle.set_num_threads(host_threads)
 
     m, n, k, sa, sb, dname, seed, desc = WORKLOADS[args.workload]
     lo, hi = shard_bounds(n, world, rank)
@@ -239,6 +425,8 @@ def main():
     ctx = maize_b200.Context(local_rank)
     if args.force_kernel:
         ctx.set("force_kernel", args.force_kernel)
+    if args.repack:
+        ctx.set("repack_bytes", (m + ns) * ((k + 63) // 64 * 64) * 2)
     decode_pdl = args.workload == "c3" and not args.no_pdl
     if decode_pdl:
         # decode: B holds weights that nothing in the stream writes, so consecutive launches may overlap
@@ -246,15 +434,8 @@ def main():
         ctx.set("b_static", 1)
     gen = torch.Generator(device=dev)
     gen.manual_seed(seed)  # every rank draws the same A; B rows are taken from a per-rank stream
-
-    def draw(shape, sigma, g):
-        if dname == "uniform":
-            return ((torch.rand(shape, device=dev, generator=g) * 2 - 1) * sigma).to(torch.bfloat16)
-        return (torch.randn(shape, device=dev, generator=g) * sigma).to(torch.bfloat16)
-
     gen_b = torch.Generator(device=dev)
     gen_b.manual_seed(1000 + seed * 16 + rank)
-    total_bytes = 2 * (m * k + n * k + m * n)
     rank_bytes = 2 * (m * k + ns * k + m * ns)
     # Inputs that fit in L2 would be served from it on back-to-back launches: rotate over enough
     # independent input sets that the bytes touched between two uses of a set exceed 4x L2.
@@ -265,18 +446,26 @@ def main():
         raise SystemExit("--b-layout kn is a single-GPU measurement")
     sets = []
     for _ in range(n_sets):
-        sets.append((draw((m, k), sa, gen) if rank == 0 else None, draw((k, ns) if kn else (ns, k), sb, gen_b),
+        sets.append((draw((m, k), sa, dname, dev, gen) if rank == 0 else None,
+                     draw((k, ns) if kn else (ns, k), sb, dname, dev, gen_b),
                      torch.empty((m, ns), dtype=torch.bfloat16, device=dev)))
     a_root, b_shard, c_shard = sets[0]
     gemm_call = (lambda a_, b_, c_: ctx.gemm_kn(a_, b_, out=c_)) if kn else (lambda a_, b_, c_: ctx.gemm(a_, b_, out=c_))
     op = NShardedGemm(m, n, k, slabs=args.slabs, ctx=ctx, device=dev, transport=args.transport,
-                      push_ctas=args.push_ctas, mc_stages=args.mc_stages, gemm_fn=gemm_call if kn else None)
+                      push_ctas=args.push_ctas, mc_stages=args.mc_stages, gemm_fn=gemm_call if kn else None,
+                      chain_rows=args.chain_rows, chain_streams=args.chain_streams, chain_fused=bool(args.chain_fused))
+    # A is resident on the root before the timed region (as `value` is defined); its readiness is an event
+    # recorded once here, so that the replication of a step need not wait for the previous step's GEMM
+    a_ready = None
+    if world > 1 and rank == 0 and not args.serial_steps:
+        a_ready = torch.cuda.Event()
+        a_ready.record()
     step_no = [0]
 
-    def step():
+    def step(_i=0):
         a_i, b_i, c_i = sets[step_no[0] % n_sets]
         step_no[0] += 1
-        op.run(a_i, b_i, c_i)
+        op.run(a_i, b_i, c_i, a_ready=a_ready)
 
     def sync_all():
         if world > 1:
@@ -294,8 +483,8 @@ def main():
         time.sleep(0.25)
 
     launches0 = ctx.launch_count
-    t_wall0 = time.time()
     sync_all()
+    t_wall0 = time.time()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(args.steps):
@@ -306,6 +495,7 @@ def main():
     t_wall1 = time.time()
     launches = ctx.launch_count - launches0
     ctx.poll()
+    last_set = (step_no[0] - 1) % n_sets
     per_rank_ms = [ms_total / args.steps]
     if world > 1:
         t = torch.tensor([ms_total], dtype=torch.float64, device=dev)
@@ -317,27 +507,79 @@ def main():
         lt = torch.tensor([launches], dtype=torch.int64, device=dev)
         dist.all_reduce(lt)
         launches = int(lt.item())
-    if sampler:
-        time.sleep(0.15)
-        sampler.stop()
     ms_per_step = ms_total / args.steps
     flops = 2.0 * m * n * k
     tflops = flops / (ms_per_step * 1e-3) / 1e12
+    clocks_headline = sampler.summary(t_wall0, t_wall1) if sampler else None
 
-    # kernel-only time on this rank (for the roofline): one GEMM over the rank's whole shard, A resident
+    # ---- verification, outside the timed region: sampled rows of this rank's C (the last timed step's output)
+    # against the CPU oracle fed with the ROOT's rows of A (sent with a plain NCCL broadcast, not with the path
+    # under test) and this rank's B
+    verified = None
+    if not args.no_verify and not kn:
+        marks = list(range(0, m, args.chain_rows)) + [lo_ for lo_, _ in op.slabs]
+        rows = sample_rows(m, 64, seed, marks)
+        idx = torch.from_numpy(rows).to(dev)
+        a_rows = sets[last_set][0][idx].contiguous() if rank == 0 else \
+            torch.empty((len(rows), k), dtype=torch.bfloat16, device=dev)
+        if world > 1:
+            dist.broadcast(a_rows, src=0)
+        ok, err, bound = check_rows(to_u16(a_rows), to_u16(sets[last_set][1]), to_u16(sets[last_set][2][idx]), k, host_threads)
+        v = torch.tensor([0.0 if ok else 1.0, err, bound], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(v, op=dist.ReduceOp.MAX)
+        verified = {"rows": int(len(rows)), "cols_per_rank": ns, "ranks": world, "max_err": float(v[1]),
+                    "bound": float(v[2]), "ok": bool(float(v[0]) == 0.0),
+                    "checker": "CPU oracle on sampled rows of every rank's C shard (the path's tolerance and the tight bound of the parity tests)"}
+
+    # ---- kernel time for the roofline.  N = 1: a step IS one launch of the dominant kernel, so the roofline uses the
+    # timed step loop itself; a second, identical loop is recorded beside it with its own clock samples.
+    # N > 1: one GEMM over the rank's whole shard with A resident.
     a_res = a_root if rank == 0 else op.a_buffer(b_shard)
-    reps = max(3, min(args.steps, 10)) * n_sets
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for i in range(reps):
+
+    def kernel_only(i):
         _, b_i, c_i = sets[i % n_sets]
         a_i = sets[i % n_sets][0] if rank == 0 else a_res
         gemm_call(a_i, b_i, c_i)
-    e1.record()
-    torch.cuda.synchronize()
-    kernel_ms = e0.elapsed_time(e1) / reps
-    kernel_name = ctx.pick_kernel(m // len(op.slabs) if world > 1 else m, ns, k)
+
+    reps = max(3, min(args.steps, 10)) * n_sets
+    repeat_ms, rw0, rw1 = time_loop(kernel_only, reps)
+    repeat = {"ms": repeat_ms, "reps": reps, "clocks": sampler.summary(rw0, rw1) if sampler else None}
+    kernel_ms = ms_per_step if world == 1 else repeat_ms
+    kernel_name = ctx.pick_kernel(m, ns, k)
+
+    # ---- cuBLAS through torch.matmul on the same tensors, interleaved with this library's launches (N = 1)
+    cublas = None
+    others = None
+    peaks = measured_peaks()
+    if world == 1 and not args.no_others and not kn and args.workload != "c3":
+        c_lib = torch.empty((m, ns), dtype=torch.bfloat16, device=dev)
+
+        def lib_call(i):
+            a_i, b_i, _ = sets[i % n_sets]
+            torch.matmul(a_i, b_i.t(), out=c_lib)
+        for i in range(3):
+            lib_call(i)
+        runs = []
+        loop_reps = max(args.steps, 3) * n_sets
+        for who in ("ours", "cublas", "ours", "cublas"):
+            ms_, w0_, w1_ = time_loop(kernel_only if who == "ours" else lib_call, loop_reps)
+            ck = sampler.summary(w0_, w1_) if sampler else {}
+            runs.append({"who": who, "ms": ms_, "tflops": flops / (ms_ * 1e-3) / 1e12, "sm_mhz": ck.get("sm_mhz"),
+                         "ms_x_ghz": ms_ * ck["sm_mhz"] / 1e3 if ck.get("sm_mhz") else None})
+        cublas = {"api": "torch.matmul(a, b.T, out=...) (cuBLAS), same tensors, same process, loops interleaved",
+                  "value": statistics.mean(r["tflops"] for r in runs if r["who"] == "cublas"),
+                  "ours_value": statistics.mean(r["tflops"] for r in runs if r["who"] == "ours"), "unit": "TFLOP/s",
+                  "reps_per_loop": loop_reps, "runs": runs}
+        del c_lib
+    if world == 1 and not args.no_others and args.workload == "c4" and not kn:
+        others = []
+        for name, pdl in (("c1", False), ("c2", False), ("c3", False), ("c3", True), ("c5", False), ("t", False)):
+            try:
+                others.append(brief_workload(ctx, name, dev, peaks, sampler, reps=max(args.steps, 5), pdl=pdl,
+                                             cublas=not pdl))
+            except Exception as exc:  # report, never hide
+                others.append({"workload": name, "error": repr(exc)})
 
     # ---- end to end through the host-buffer entry point (N = 1) or pinned copies + sharded step (N > 1)
     e2e = None
@@ -363,7 +605,7 @@ def main():
                 if rank == 0:
                     a_root.copy_(ha, non_blocking=True)
                 b_shard.copy_(hb, non_blocking=True)
-                op.run(a_root, b_shard, c_shard)
+                op.run(a_root, b_shard, c_shard)  # A arrives on this stream: stream order says when it is ready
                 hc.copy_(c_shard, non_blocking=True)
 
         e2e_step()
@@ -390,9 +632,10 @@ def main():
     except Exception as exc:  # report, never hide
         e2e = {"value": None, "unit": "TFLOP/s", "error": repr(exc)}
 
+    if sampler:
+        sampler.stop()
+    failed = verified is not None and not verified["ok"]
     if rank == 0:
-        peaks = measured_peaks()
-        clocks = sampler.summary(t_wall0, t_wall1) if sampler else None
         k_flops = 2.0 * m * ns * k
         hbm_bound = args.workload == "c3"
         if hbm_bound:
@@ -400,17 +643,24 @@ def main():
             achieved = k_bytes / (kernel_ms * 1e-3) / 1e9
             roof = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                     "frac": achieved / peaks["hbm_gbs"], "traffic": None,
-                    "peak_source": f"{peaks['source']} STREAM-style copy"}
+                    "peak_source": f"{peaks['source']} STREAM-style copy", "frac_of_spec_8TBs": achieved / SPEC_HBM_GBS}
         else:
             achieved = k_flops / (kernel_ms * 1e-3) / 1e12
             long_run = ms_total > 2000.0
             peak = peaks["bf16_tflops_sustained"] if long_run else peaks["bf16_tflops"]
             roof = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                     "frac": achieved / peak, "traffic": None,
-                    "peak_source": f"{peaks['source']} cuBLAS bf16 " + ("sustained" if long_run else "burst")}
-        roof["traffic"] = NCU_TRAFFIC.get(args.workload) if world == 1 else None
+                    "peak_source": f"{peaks['source']} cuBLAS bf16 " + ("sustained" if long_run else "burst"),
+                    "frac_of_sustained": achieved / peaks["bf16_tflops_sustained"],
+                    "frac_of_spec_2250": achieved / SPEC_TFLOPS}
+        if world == 1 and args.workload in NCU_TRAFFIC:
+            roof["traffic"] = NCU_TRAFFIC[args.workload][0]
+            roof["traffic_source"] = "one ncu capture of this kernel on this workload, " + NCU_TRAFFIC[args.workload][1]
         roof["kernel"] = kernel_name
         roof["kernel_ms"] = kernel_ms
+        roof["kernel_ms_source"] = "the timed step loop (one launch per step)" if world == 1 else \
+            "a loop of whole-shard launches with A resident, after the timed region"
+        roof["repeat_loop"] = repeat
         cpu = None
         if world == 1 and not args.no_cpu_baseline:
             r = cpu_sample(args.workload, seconds=args.cpu_seconds)
@@ -421,24 +671,18 @@ def main():
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "bf16 in, fp32 accumulate", "data": "synthetic",
-            "config": {"workload": f"{args.workload}: {desc}", "M": m, "N": n, "K": k,
-                       "layout": "A MxK row-major, B KxN row-major, C MxN bf16" if kn else
-                                 "A MxK row-major, B NxK K-major, C MxN bf16",
-                       "parallelism": "single GPU" if world == 1 else
-                                      f"N-sharded x{world}, A replicated from rank 0 in {len(op.slabs)} row slabs over "
-                                      + {"multimem": "NVSwitch multicast (multimem.st push kernel)",
-                                         "chain": "a copy-engine chain (rank r forwards to r+1 in 1024-row chunks)",
-                                         "nccl": "NCCL broadcast"}[op.transport],
-                       "l2": (f"rotating over {n_sets} independent input sets ({n_sets * rank_bytes >> 20} MiB > 4x L2), "
-                              "back-to-back launches") if small else "inputs exceed L2 (back-to-back launches)",
-                       "algorithmic_bytes": total_bytes, "ms_per_step_by_rank": per_rank_ms,
-                       "launch": "programmatic dependent launch, B declared static (weights)" if decode_pdl else "plain"},
-            "roofline": roof, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
+            "config": config_for(args, world), "ms_per_step_by_rank": per_rank_ms,
+            "transport": op.transport if world > 1 else None,
+            "verified": verified, "roofline": roof, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches,
+            "clocks": clocks_headline, "cublas_same_run": cublas, "others": others,
         }
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+    if failed:
+        sys.stderr.write(f"bench: verification against the CPU oracle FAILED: {verified}\n")
+        sys.exit(3)
 
 
 if __name__ == "__main__":

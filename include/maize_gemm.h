@@ -24,8 +24,10 @@
  * 2-byte alignment and any N.
  *
  * Every call enqueues work on the caller's CUDA stream and returns without
- * synchronising; no call allocates device memory except maize_ctx_create and
- * the *_host entry point (which grows a cached staging area on first use).
+ * synchronising; no call allocates device memory except maize_ctx_create,
+ * maize_ctx_set("profile" / "repack_bytes") and the *_host entry point (which
+ * waits for the stream, frees and re-allocates its cached staging area whenever
+ * a call needs more than the last one did, and waits for C before it returns).
  * Nothing here ever traps or asserts on the device: a device wait that runs
  * out of its time budget records MAIZE_ERR_TIMEOUT in a status word that
  * maize_ctx_poll reads back.
@@ -158,8 +160,12 @@ MAIZE_API maize_status_t maize_ctx_poll(maize_ctx_t *ctx, void *cuda_stream);
  * kernels of the multi-GPU path, default 512), "pdl" (1 = launch the decode kernel with programmatic
  * stream serialization, so that it may start while the stream's previous kernel drains), "b_static"
  * (1 = the caller guarantees that no earlier work of the stream writes B, e.g. inference weights; with
- * "pdl" the kernel then fetches its first B tiles before waiting for that earlier work), "debug_flags"
- * (performance diagnostics that make results WRONG: 1 = all loads hit one tile, 2 = no loads). */
+ * "pdl" the kernel then fetches its first B tiles before waiting for that earlier work), "chain_streams"
+ * (1 or 2: streams that maize_chain_forward alternates its chunks between), "repack_bytes" (size of an
+ * optional scratch, allocated by this call, into which operands whose row pitch is not a multiple of 128
+ * bytes are copied with an aligned pitch ahead of a large GEMM; 0 frees it), "debug_flags"
+ * (performance diagnostics that make results WRONG: 1 = all loads hit one tile, 2 = no loads; refused
+ * unless "profile" is 1, cleared when "profile" returns to 0). */
 MAIZE_API maize_status_t maize_ctx_set(maize_ctx_t *ctx, const char *key, int64_t value);
 /* Reads back any key of maize_ctx_set, plus "sm_count" and "device". */
 MAIZE_API maize_status_t maize_ctx_get(const maize_ctx_t *ctx, const char *key, int64_t *value);
@@ -223,7 +229,8 @@ MAIZE_API maize_status_t maize_copy_async(maize_ctx_t *ctx, void *dst, const voi
  * in ascending groups of rows (see "group_rows"), each CTA's loader waits for its tile's rows, and the wait is
  * bounded like every other: if the count does not arrive within "timeout_ns" the kernel ends and
  * maize_ctx_poll returns MAIZE_ERR_TIMEOUT (C is then incomplete).  Decode-shaped problems run on the tiled
- * kernels here.  No reference counterpart (the reference is single-GPU, crates/maize_tile/src/gemm.rs:110). */
+ * kernels here.  No reference counterpart (the reference is single-GPU: its GEMM entry point, crates/maize_tile/src/gemm/mod.rs:37-55, takes one
+ * device's panels). */
 MAIZE_API maize_status_t maize_gemm_bf16_gated(maize_ctx_t *ctx, const void *a, uint64_t lda, const void *b,
                                                uint64_t ldb, void *c, uint64_t ldc, uint32_t m, uint32_t n, uint32_t k,
                                                const void *rows_landed, uint32_t landed_base, uint32_t rows_per_count,
@@ -232,7 +239,8 @@ MAIZE_API maize_status_t maize_gemm_bf16_gated(maize_ctx_t *ctx, const void *a, 
  * (i = 0, 1, ...) wait (bounded, if `wait_flag` is not NULL) until the local word `wait_flag` has reached
  * first_value + i, copy the chunk to `dst` + its offset (copy engines; `dst` is the next rank's landing buffer
  * through its peer mapping), then store first_value + i in `dst_flag` (the next rank's "chunks landed" word).
- * Everything is enqueued on `cuda_stream` in one call. */
+ * Everything is enqueued in one call, on `cuda_stream` and, with "chain_streams" = 2, alternately on a helper
+ * stream of the context that forks from and joins `cuda_stream` (counts are still published in chunk order). */
 MAIZE_API maize_status_t maize_chain_forward(maize_ctx_t *ctx, const void *wait_flag, uint32_t first_value, void *dst,
                                              const void *src, uint64_t total_bytes, uint64_t chunk_bytes,
                                              void *dst_flag, void *cuda_stream);
@@ -264,8 +272,11 @@ MAIZE_API maize_status_t maize_debug_wait_expires(maize_ctx_t *ctx, uint64_t bud
  * 16-byte aligned.  Anything beyond is refused with MAIZE_ERR_UNSUPPORTED and a message in `errbuf`
  * that states what was needed and what the scratch holds; use maize_gemm_bf16 with a context then.
  *
- * The FIRST call on each device looks up the array's device address, the SM count and the tensor-map
- * encoder and sets the kernel's shared-memory limit; make that first call before any stream capture.
+ * The FIRST call on each device is a start-up step: it looks up the array's device address, the SM count
+ * and the tensor-map encoder and sets the kernel's shared-memory limit, and if the library's GPU code has not
+ * been loaded on that device yet, the CUDA runtime loads it then, which is when the driver reserves the array
+ * (and may fail for lack of memory).  Make that first call at start-up, before any stream capture; only the
+ * calls after it are free of allocation.  K == 0 sets C to zero, as in maize_gemm_bf16.
  * Every call on a device uses the same array and finds what the previous call left there: the
  * counters and the status word are cleared on `cuda_stream` before each launch.  Calls whose kernels
  * could overlap on the GPU (different streams without a dependency) race on the array: order them.

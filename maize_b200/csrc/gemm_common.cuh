@@ -241,17 +241,28 @@ __device__ __forceinline__ void drain_accumulator(const GemmParams &p, uint8_t *
     }
 }
 
-// Copies a row-major matrix of `rows` x (16 * cols16) bytes to another row pitch, 16 bytes per thread and step.
+// Copies up to two row-major matrices of `rows` x (16 * cols16) bytes to another row pitch, 16 bytes per thread and
+// step, in one launch (segment 0 takes the first `rows0` values of the row index, segment 1 the rest).
 // Used ahead of the GEMM for operands whose pitch is not a multiple of 128 bytes: every 128-byte row of a TMA
 // box then straddles two lines, which was measured to cost a third of the GEMM's rate (4111 x 3967 x 4104: 0.164 ms
 // with pitch 8208 B, 0.108 ms with 8320 B); a pre-pass costs two passes over the operand at the HBM rate.
-__global__ void repack_rows_kernel(const uint4 *__restrict__ src, uint64_t src_pitch16, uint4 *__restrict__ dst,
-                                   uint64_t dst_pitch16, uint32_t rows, uint32_t cols16)
+struct RepackSegment {
+    const uint4 *src;
+    uint4 *dst;
+    uint64_t src_pitch16, dst_pitch16;  // row pitches in 16-byte units
+    uint32_t rows;
+};
+
+__global__ void __launch_bounds__(256) repack_rows_kernel(RepackSegment s0, RepackSegment s1, uint32_t cols16)
 {
-    // blockIdx.y strides over rows, x over the 16-byte columns of a row
-    for (uint32_t r = blockIdx.y; r < rows; r += gridDim.y) {
-        const uint4 *s = src + static_cast<uint64_t>(r) * src_pitch16;
-        uint4 *d = dst + static_cast<uint64_t>(r) * dst_pitch16;
+    // blockIdx.y strides over the rows of both segments, x over the 16-byte columns of a row
+    const uint32_t total = s0.rows + s1.rows;
+    for (uint32_t r = blockIdx.y; r < total; r += gridDim.y) {
+        const bool first = r < s0.rows;
+        const RepackSegment &g = first ? s0 : s1;
+        const uint32_t row = first ? r : r - s0.rows;
+        const uint4 *s = g.src + static_cast<uint64_t>(row) * g.src_pitch16;
+        uint4 *d = g.dst + static_cast<uint64_t>(row) * g.dst_pitch16;
         for (uint32_t c = blockIdx.x * blockDim.x + threadIdx.x; c < cols16; c += gridDim.x * blockDim.x)
             d[c] = s[c];
     }

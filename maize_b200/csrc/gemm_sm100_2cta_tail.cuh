@@ -132,11 +132,14 @@ gemm_bf16_sm100_2cta_tail(const __grid_constant__ CUtensorMap tma_a, const __gri
             uint32_t stage = 0, phase = 0;
             bool ok = true;
             const uint64_t pol = ptx::policy_evict_normal();
+            int32_t gate_seen = 0;
             TailWork w;
             for (uint32_t i = 0; ok && tail_work(tp, pair, num_pairs, num_steps, i, w); ++i) {
                 const TileCoord tc = tile_coord(w.tile, p.tiles_m, p.tiles_n, p.group_m);
                 const int32_t m0 = static_cast<int32_t>(tc.m_blk * kPairBlockM + cta_rank * kBlockM);
                 const int32_t n0 = static_cast<int32_t>(tc.n_blk * BN + cta_rank * (BN / 2));
+                if (!(ok = gate_rows_landed(p, static_cast<uint32_t>(m0) + kBlockM, gate_seen, ctl)))
+                    break;
                 for (uint32_t step = w.step_lo; step < w.step_hi; ++step) {
                     ok = wait_bounded<true>(empty_bar(stage), phase ^ 1u, ctl, 1);
                     if (!ok)

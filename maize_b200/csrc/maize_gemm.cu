@@ -63,6 +63,7 @@ constexpr int kNumVariants = static_cast<int>(sizeof(kVariants) / sizeof(kVarian
 constexpr int kMaxProfileCtas = 1024;
 constexpr int kMaxHostSlabs = 16;  // row slabs of A / C that the host entry point pipelines over PCIe
 constexpr size_t kPartialsBytes = size_t(32) << 20;  // stream-K scratch per context
+constexpr size_t kDefaultRepackBytes = size_t(128) << 20;  // scratch of the pitch-aligning pre-pass per context
 constexpr uint32_t kMaxSkinnyTiles = 65536;          // 4 counters each; N up to 8M rows
 
 class DeviceGuard {
@@ -99,6 +100,8 @@ struct maize_ctx {
     uint32_t pdl = 0;       // launch the decode kernel with programmatic stream serialization
     uint32_t b_static = 0;  // the caller guarantees that nothing earlier in the stream writes B (weights)
     uint32_t push_threads = 512;  // threads per CTA of the copy kernels of the multi-GPU path
+    uint32_t tma_promotion = 3;   // CUtensorMapL2promotion of the operand maps: 0 none, 1 64 B, 2 128 B, 3 256 B
+    uint32_t tail_split = 1;      // split the last partial round of pair tiles along K when pairs would idle
     uint32_t chain_streams = 1;   // 2: maize_chain_forward alternates chunks between the caller's stream and a helper
     cudaStream_t chain_helper = nullptr;
     cudaEvent_t chain_ev[3] = {};  // [0], [1]: "chunk published" per stream; [2]: fork / join
@@ -108,6 +111,9 @@ struct maize_ctx {
     size_t staging_bytes = 0;
     void *repack = nullptr;  // scratch for operands copied to a 128-byte-aligned pitch ("repack_bytes")
     size_t repack_bytes = 0;
+    const void *repack_b_ptr = nullptr;  // B whose aligned-pitch copy sits at the front of `repack` ("b_static" only)
+    uint32_t repack_b_rows = 0, repack_b_cols = 0;
+    uint64_t repack_b_ld = 0;
     // helper streams and events of the *_host entry point (created on first use)
     cudaStream_t copy_in = nullptr, copy_out = nullptr;
     cudaEvent_t ev_start = nullptr, ev_done = nullptr;
@@ -147,7 +153,7 @@ maize_status_t make_operand_map(maize_ctx_t *ctx, CUtensorMap *map, const void *
     cuuint32_t estride[2] = {1, 1};
     CUresult r = ctx->encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(base), gdim, gstride, box,
                              estride, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                             static_cast<CUtensorMapL2promotion>(ctx->tma_promotion), CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
         char buf[160];
         snprintf(buf, sizeof buf, "cuTensorMapEncodeTiled failed (CUresult %d) for %llu x %llu, ld %llu", (int)r,
@@ -439,34 +445,52 @@ maize_status_t gemm_impl(maize_ctx_t *ctx, const void *a, uint64_t lda, const vo
     }
 
     // Operand pitches that are not multiples of 128 bytes: copy the operand to an aligned pitch first when the
-    // caller has provided scratch for it ("repack_bytes") and the GEMM is long enough for the copy to pay
-    // (the loads of a misaligned operand cost about a third of the GEMM's time; the copy moves 4 bytes per element
-    // at ~6 TB/s plus a launch).
+    // context holds scratch for it ("repack_bytes") and the GEMM is long enough for the copy to pay (the loads of
+    // a misaligned operand cost about a third of the GEMM's time; the copy moves 4 bytes per element at ~6 TB/s
+    // plus a launch).  B goes to the front of the scratch; with "b_static" (nothing writes B: weights) the copy
+    // of B is kept and reused by later calls with the same B.
     if (ctx->repack && !b_kn) {
         const uint64_t pitch = (uint64_t(k) + 63) / 64 * 64;  // elements; a multiple of 128 bytes
         const bool fix_a = (lda * 2) % 128 != 0 && !gate;     // a gated A is still arriving: leave it
         const bool fix_b = (ldb * 2) % 128 != 0;
+        const bool b_cached = fix_b && ctx->b_static && ctx->repack_b_ptr == b && ctx->repack_b_rows == n &&
+                              ctx->repack_b_cols == k && ctx->repack_b_ld == ldb;
         const double gemm_us = 2.0 * m * n * k / 1.3e9;       // at 1300 TFLOP/s
-        const double copy_us = ((fix_a ? m : 0) + (fix_b ? n : 0)) * double(k) * 4.0 / 6.0e6 + 4.0;
-        const size_t need = (size_t(fix_a ? m : 0) + size_t(fix_b ? n : 0)) * pitch * 2;
+        const double copy_us = ((fix_a ? m : 0) + (fix_b && !b_cached ? n : 0)) * double(k) * 4.0 / 6.0e6 + 4.0;
+        const size_t b_bytes = fix_b ? size_t(n) * pitch * 2 : 0;
+        const size_t need = b_bytes + (fix_a ? size_t(m) * pitch * 2 : 0);
         if ((fix_a || fix_b) && need <= ctx->repack_bytes && copy_us < 0.3 * gemm_us) {
-            char *dst = static_cast<char *>(ctx->repack);
-            auto repack = [&](const void *&ptr, uint64_t &ld, uint32_t rows) {
-                const dim3 grid((k / 8 + 255) / 256 < 4 ? (k / 8 + 255) / 256 : 4, rows < 65535u ? rows : 65535u);
-                maize::repack_rows_kernel<<<grid, 256, 0, stream>>>(static_cast<const uint4 *>(ptr), ld / 8,
-                                                                    reinterpret_cast<uint4 *>(dst), pitch / 8, rows, k / 8);
-                ptr = dst;
-                ld = pitch;
-                dst += size_t(rows) * pitch * 2;
+            char *base = static_cast<char *>(ctx->repack);
+            maize::RepackSegment seg[2] = {};
+            int nseg = 0;
+            if (fix_b) {
+                if (!b_cached) {
+                    seg[nseg++] = {static_cast<const uint4 *>(b), reinterpret_cast<uint4 *>(base), ldb / 8, pitch / 8, n};
+                    ctx->repack_b_ptr = ctx->b_static ? b : nullptr;
+                    ctx->repack_b_rows = n;
+                    ctx->repack_b_cols = k;
+                    ctx->repack_b_ld = ldb;
+                }
+                b = base;
+                ldb = pitch;
+            } else if (fix_a) {
+                ctx->repack_b_ptr = nullptr;  // A is about to overwrite the front of the scratch
+            }
+            if (fix_a) {
+                seg[nseg++] = {static_cast<const uint4 *>(a), reinterpret_cast<uint4 *>(base + b_bytes), lda / 8, pitch / 8, m};
+                a = base + b_bytes;
+                lda = pitch;
+            }
+            if (nseg > 0) {
+                const uint32_t rows = seg[0].rows + seg[1].rows;
+                const uint32_t gx = (k / 8 + 255) / 256 < 4 ? (k / 8 + 255) / 256 : 4;
+                const dim3 rgrid(gx ? gx : 1, rows < 65535u ? rows : 65535u);
+                maize::repack_rows_kernel<<<rgrid, 256, 0, stream>>>(seg[0], seg[1], k / 8);
                 ctx->launches += 1;
-            };
-            if (fix_a)
-                repack(a, lda, m);
-            if (fix_b)
-                repack(b, ldb, n);
-            cudaError_t er = cudaGetLastError();
-            if (er != cudaSuccess)
-                return fail_cuda(ctx, "kernel launch", er);
+                cudaError_t er = cudaGetLastError();
+                if (er != cudaSuccess)
+                    return fail_cuda(ctx, "kernel launch", er);
+            }
         }
     }
 
@@ -515,9 +539,11 @@ maize_status_t gemm_impl(maize_ctx_t *ctx, const void *a, uint64_t lda, const vo
         cudaMemsetAsync(ctx->d_profile, 0, sizeof(unsigned long long) * maize::kProfileSlots * kMaxProfileCtas, stream);
     }
 
-    if (vi == kPairTail) {
-        if (b_kn || gate)
-            return fail(ctx, MAIZE_ERR_UNSUPPORTED, "the tail-split kernel takes neither a K x N matrix B nor a row gate");
+    // The CTA-pair kernel whose last, partial round of tiles is split along K: chosen whenever the split is more
+    // than 1 (idle pairs in the last round and a K long enough to cut), or forced by id.
+    if ((vi == kPairWide && ctx->tail_split && !b_kn) || vi == kPairTail) {
+        if (b_kn)
+            return fail(ctx, MAIZE_ERR_UNSUPPORTED, "the tail-split kernel does not take a K x N matrix B");
         // P pairs run full_rounds rounds of whole tiles; the remaining tiles are cut into `split` k-ranges each,
         // as many as there are idle pairs, but never fewer than 8 k-steps of 128 per part
         const uint32_t pairs = cap;  // all pairs, also when there are fewer tiles than pairs: those get split too
@@ -539,23 +565,25 @@ maize_status_t gemm_impl(maize_ctx_t *ctx, const void *a, uint64_t lda, const vo
             if (s > 1 && tp.tail_tiles * 8u <= 4u * kMaxSkinnyTiles)
                 tp.split = s;
         }
-        tp.partials = ctx->d_partials;
-        tp.counters = ctx->d_counters;
-        auto kernel = maize::gemm_bf16_sm100_2cta_tail<2, 3>;
-        const uint32_t smem = maize::PairSmemLayout<256, 2, 3>::kDynamicBytes;
-        if (!ctx->attr_set[vi]) {
-            cudaError_t ea = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-            if (ea != cudaSuccess)
-                return fail_cuda(ctx, "cudaFuncSetAttribute(max dynamic smem)", ea);
-            ctx->attr_set[vi] = true;
+        if (tp.split > 1 || vi == kPairTail) {
+            tp.partials = ctx->d_partials;
+            tp.counters = ctx->d_counters;
+            auto kernel = maize::gemm_bf16_sm100_2cta_tail<2, 3>;
+            const uint32_t smem = maize::PairSmemLayout<256, 2, 3>::kDynamicBytes;
+            if (!ctx->attr_set[kPairTail]) {
+                cudaError_t ea = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+                if (ea != cudaSuccess)
+                    return fail_cuda(ctx, "cudaFuncSetAttribute(max dynamic smem)", ea);
+                ctx->attr_set[kPairTail] = true;
+            }
+            const uint64_t busy = tp.full_rounds > 0 ? pairs : uint64_t(tp.tail_tiles) * tp.split;
+            kernel<<<static_cast<uint32_t>(2 * busy), maize::kNumThreads, smem, stream>>>(ta, tb, tp);
+            cudaError_t el = cudaGetLastError();
+            if (el != cudaSuccess)
+                return fail_cuda(ctx, "kernel launch", el);
+            ctx->launches += 1;
+            return MAIZE_OK;
         }
-        const uint64_t busy = tp.full_rounds > 0 ? pairs : uint64_t(tp.tail_tiles) * tp.split;
-        kernel<<<static_cast<uint32_t>(2 * busy), maize::kNumThreads, smem, stream>>>(ta, tb, tp);
-        cudaError_t el = cudaGetLastError();
-        if (el != cudaSuccess)
-            return fail_cuda(ctx, "kernel launch", el);
-        ctx->launches += 1;
-        return MAIZE_OK;
     }
     if (b_kn) {
         switch (vi) {
@@ -648,10 +676,12 @@ maize_status_t maize_ctx_create(int device, maize_ctx_t **out)
         cudaMemset(ctx->d_push_counter, 0, sizeof(unsigned int) * 32) != cudaSuccess ||
         cudaMalloc(&ctx->d_counters, sizeof(unsigned int) * 4 * kMaxSkinnyTiles) != cudaSuccess ||
         cudaMemset(ctx->d_counters, 0, sizeof(unsigned int) * 4 * kMaxSkinnyTiles) != cudaSuccess ||
-        cudaMallocHost(&ctx->h_status, sizeof(DeviceStatus)) != cudaSuccess) {
+        cudaMallocHost(&ctx->h_status, sizeof(DeviceStatus)) != cudaSuccess ||
+        cudaMalloc(&ctx->repack, kDefaultRepackBytes) != cudaSuccess) {
         maize_ctx_destroy(ctx);
         return MAIZE_ERR_CUDA;
     }
+    ctx->repack_bytes = kDefaultRepackBytes;
     *out = ctx;
     return MAIZE_OK;
 }
@@ -886,6 +916,11 @@ maize_status_t maize_ctx_poll(maize_ctx_t *ctx, void *cuda_stream)
     const DeviceStatus s = *ctx->h_status;
     if (s.code == maize::kStatusOk)
         return MAIZE_OK;
+    // A launch that gave up on a wait may have left arrival counters of the stream-K exchange or of the push
+    // kernels half-way; the next launch must find them at zero again, or it would combine stale partial sums.
+    cudaMemsetAsync(ctx->d_counters, 0, sizeof(unsigned int) * 4 * kMaxSkinnyTiles, stream);
+    cudaMemsetAsync(ctx->d_push_counter, 0, sizeof(unsigned int) * 32, stream);
+    cudaStreamSynchronize(stream);
     char buf[128];
     snprintf(buf, sizeof buf, "device status %d raised by role %d of CTA %d", s.code, s.role, s.cta);
     ctx->err = buf;
@@ -915,12 +950,14 @@ maize_status_t maize_ctx_set(maize_ctx_t *ctx, const char *key, int64_t value)
             cudaDeviceSynchronize();
             cudaFree(ctx->d_profile);
             ctx->d_profile = nullptr;
+            ctx->debug_flags = 0;
         }
     } else if (!strcmp(key, "repack_bytes")) {
         // Scratch for the pitch-aligning pre-pass (0 frees it).  Allocated here, never inside a GEMM call.
         if (value < 0)
             return fail(ctx, MAIZE_ERR_INVALID_ARG, "repack_bytes must be >= 0");
         DeviceGuard guard(ctx->device);
+        ctx->repack_b_ptr = nullptr;
         if (ctx->repack) {
             cudaDeviceSynchronize();
             cudaFree(ctx->repack);
@@ -941,6 +978,13 @@ maize_status_t maize_ctx_set(maize_ctx_t *ctx, const char *key, int64_t value)
         ctx->pdl = value ? 1u : 0u;
     } else if (!strcmp(key, "b_static")) {
         ctx->b_static = value ? 1u : 0u;
+        ctx->repack_b_ptr = nullptr;  // a kept copy of B is only valid while the promise holds
+    } else if (!strcmp(key, "tma_promotion")) {
+        if (value < 0 || value > 3)
+            return fail(ctx, MAIZE_ERR_INVALID_ARG, "tma_promotion: 0 (none), 1 (64 B), 2 (128 B) or 3 (256 B)");
+        ctx->tma_promotion = static_cast<uint32_t>(value);
+    } else if (!strcmp(key, "tail_split")) {
+        ctx->tail_split = value ? 1u : 0u;
     } else if (!strcmp(key, "chain_streams")) {
         if (value != 1 && value != 2)
             return fail(ctx, MAIZE_ERR_INVALID_ARG, "chain_streams: 1 or 2");
@@ -950,6 +994,9 @@ maize_status_t maize_ctx_set(maize_ctx_t *ctx, const char *key, int64_t value)
             return fail(ctx, MAIZE_ERR_INVALID_ARG, "push_threads: a multiple of 32 in [32, 512]");
         ctx->push_threads = static_cast<uint32_t>(value);
     } else if (!strcmp(key, "debug_flags")) {
+        // these switches make results wrong on purpose; they are honoured only while "profile" is on
+        if (value != 0 && !ctx->d_profile)
+            return fail(ctx, MAIZE_ERR_INVALID_ARG, "debug_flags may only be set while \"profile\" is 1");
         ctx->debug_flags = static_cast<uint32_t>(value);
     } else if (!strcmp(key, "max_ctas")) {
         if (value < 0)
@@ -987,6 +1034,14 @@ maize_status_t maize_ctx_get(const maize_ctx_t *ctx, const char *key, int64_t *v
         *value = ctx->debug_flags;
     else if (!strcmp(key, "profile"))
         *value = ctx->d_profile ? 1 : 0;
+    else if (!strcmp(key, "chain_streams"))
+        *value = ctx->chain_streams;
+    else if (!strcmp(key, "tail_split"))
+        *value = ctx->tail_split;
+    else if (!strcmp(key, "tma_promotion"))
+        *value = ctx->tma_promotion;
+    else if (!strcmp(key, "repack_bytes"))
+        *value = static_cast<int64_t>(ctx->repack_bytes);
     else
         return MAIZE_ERR_INVALID_ARG;
     return MAIZE_OK;
@@ -1366,8 +1421,21 @@ extern "C" maize_status_t maize_gemm_bf16_skinny_static(const void *a, uint32_t 
     const uint32_t m = a_rows, n = b_rows, k = a_cols;
     if (m == 0 || n == 0)
         return MAIZE_OK;
-    if (!a || !b || !c || k == 0) {
-        put_error(errbuf, errbuf_len, "null pointer or K == 0");
+    if (!c) {
+        put_error(errbuf, errbuf_len, "C pointer is null");
+        return MAIZE_ERR_INVALID_ARG;
+    }
+    if (k == 0) {
+        // empty sum, as in maize_gemm_bf16: C = 0 (a memset on the caller's stream allocates nothing)
+        cudaError_t ez = cudaMemsetAsync(c, 0, size_t(m) * n * 2, static_cast<cudaStream_t>(cuda_stream));
+        if (ez != cudaSuccess) {
+            put_error(errbuf, errbuf_len, std::string("cudaMemsetAsync: ") + cudaGetErrorString(ez));
+            return MAIZE_ERR_CUDA;
+        }
+        return MAIZE_OK;
+    }
+    if (!a || !b) {
+        put_error(errbuf, errbuf_len, "A or B pointer is null");
         return MAIZE_ERR_INVALID_ARG;
     }
     if (m > 32) {

@@ -75,43 +75,45 @@ __device__ __forceinline__ bool flag_wait_bounded(const uint32_t *flag, uint32_t
 // Copies n16 16-byte units from local `src` to every replica behind `mc_dst`; the last CTA to
 // finish publishes `flag_value` at `mc_flag` on every GPU.  `done_counter` is zero between launches.
 // If `wait_flag` is not null the copy first waits (bounded) for *wait_flag >= wait_value: the source
-// is then itself a landing area that another GPU is still filling.  A wait that expires skips the
-// copy and the flag, so that nobody consumes bytes that never arrived; the status word reports it.
+// is then itself a landing area that another GPU is still filling.  A CTA whose wait expires skips its
+// part of the copy, and the flag is then not published, so that nobody consumes bytes that never arrived;
+// the status word reports it.  The grid has at most 65535 CTAs (the host caps it far below).
 __global__ void __launch_bounds__(512) mc_push_kernel(const uint4 *src, uint4 *mc_dst, uint64_t n16,
                                                       unsigned int *done_counter, uint32_t *mc_flag,
                                                       uint32_t flag_value, const uint32_t *wait_flag,
                                                       uint32_t wait_value, DeviceStatus *status, uint64_t budget_ns)
 {
-    if (wait_flag != nullptr) {
-        __shared__ int landed;
-        if (threadIdx.x == 0)
-            landed = flag_wait_bounded(wait_flag, wait_value, status, budget_ns, 7) ? 1 : 0;
-        __syncthreads();
-        if (!landed)
-            return;
+    __shared__ int landed;
+    if (threadIdx.x == 0)
+        landed = (wait_flag == nullptr || flag_wait_bounded(wait_flag, wait_value, status, budget_ns, 7)) ? 1 : 0;
+    __syncthreads();
+    if (landed) {
+        const uint64_t pol = ptx::policy_evict_first();
+        const uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
+        uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+        for (; i + 3 * stride < n16; i += 4 * stride) {
+            // plain (coherent) loads: the source may have been written by another GPU moments ago
+            const uint4 v0 = ld_stream(src + i, pol), v1 = ld_stream(src + i + stride, pol),
+                        v2 = ld_stream(src + i + 2 * stride, pol), v3 = ld_stream(src + i + 3 * stride, pol);
+            multimem_st_v4(mc_dst + i, v0);
+            multimem_st_v4(mc_dst + i + stride, v1);
+            multimem_st_v4(mc_dst + i + 2 * stride, v2);
+            multimem_st_v4(mc_dst + i + 3 * stride, v3);
+        }
+        for (; i < n16; i += stride)
+            multimem_st_v4(mc_dst + i, ld_stream(src + i, pol));
     }
-    const uint64_t pol = ptx::policy_evict_first();
-    const uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
-    uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-    for (; i + 3 * stride < n16; i += 4 * stride) {
-        // plain (coherent) loads: the source may have been written by another GPU moments ago
-        const uint4 v0 = ld_stream(src + i, pol), v1 = ld_stream(src + i + stride, pol), v2 = ld_stream(src + i + 2 * stride, pol),
-                    v3 = ld_stream(src + i + 3 * stride, pol);
-        multimem_st_v4(mc_dst + i, v0);
-        multimem_st_v4(mc_dst + i + stride, v1);
-        multimem_st_v4(mc_dst + i + 2 * stride, v2);
-        multimem_st_v4(mc_dst + i + 3 * stride, v3);
-    }
-    for (; i < n16; i += stride)
-        multimem_st_v4(mc_dst + i, ld_stream(src + i, pol));
     __syncthreads();
     if (threadIdx.x == 0) {
+        // Every CTA arrives, also one whose wait ran out (it marks the upper half of the counter), so that the
+        // counter is back at zero for the next launch whatever happened; the flag is published only if all copied.
         __threadfence_system();
-        const unsigned int arrived = atomicAdd(done_counter, 1u);
-        if (arrived == gridDim.x - 1) {
+        const unsigned int arrived = atomicAdd(done_counter, landed ? 1u : 0x10001u);
+        if ((arrived & 0xffffu) == gridDim.x - 1) {
             *done_counter = 0u;
             __threadfence_system();
-            multimem_st_release_u32(mc_flag, flag_value);
+            if (landed && (arrived >> 16) == 0u)
+                multimem_st_release_u32(mc_flag, flag_value);
         }
     }
 }

@@ -264,8 +264,18 @@ def gemm_skinny_static(a, b, out, stream=None, device_status=None):
     on the GPU share the array and must be ordered by the caller.  ``device_status``: optional int32[4]
     CUDA tensor that receives a timeout code.
     """
+    import torch
     lib = _ffi.load()
     err = ctypes.create_string_buffer(256)
+    # the C entry assumes dense rows (lda = ldb = K, ldc = N) on the current device: check before handing out pointers
+    cur = torch.cuda.current_device()
+    for name, t in (("a", a), ("b", b), ("out", out)):
+        if (t.dim() != 2 or t.dtype != torch.bfloat16 or not t.is_cuda or t.device.index != cur
+                or (t.shape[1] > 1 and t.stride(1) != 1) or (t.shape[0] > 1 and t.stride(0) != t.shape[1])):
+            raise MaizeError(_ffi.INVALID_ARG, f"{name}: expected a dense 2-D bfloat16 tensor on the current CUDA device")
+    if device_status is not None and (device_status.dtype != torch.int32 or device_status.numel() < 4
+                                      or not device_status.is_cuda or not device_status.is_contiguous()):
+        raise MaizeError(_ffi.INVALID_ARG, "device_status: expected a contiguous int32 CUDA tensor of at least 4 elements")
     m, k = a.shape
     n, kb = b.shape
     st = lib.maize_gemm_bf16_skinny_static(a.data_ptr(), m, k, b.data_ptr(), n, kb, out.data_ptr(), out.shape[0],

@@ -22,13 +22,14 @@ up, else ``nccl``):
   use no shared memory and few registers, so their CTAs are co-resident with the persistent
   GEMM's.  Landing buffers are double-buffered across steps; ranks acknowledge a finished step
   in the root's memory so that nothing overwrites a buffer that is still being read.
-* ``chain`` (needs symmetric memory; the default where available): rank r forwards A to rank r+1 in chunks of 1024 rows with copy-engine copies into the next
-  rank's landing buffer (no SM touches the bytes), each followed by a flag store; a rank forwards a chunk as
-  soon as its own copy of it has landed, so all links of the chain are busy at once and every hop runs at the
-  unicast NVLink rate.  GEMM launches wait for the chunks that cover their slab.  Options (off by default):
-  ``chain_in_library`` enqueues a step's forwarding with one library call, ``chain_rows`` sets the chunk size,
-  ``chain_fused`` runs ONE gated GEMM launch per step on the receiving ranks, whose loaders wait inside the
-  kernel for the chunk count of their tile's rows.
+* ``chain`` (needs symmetric memory; the default where available): rank r forwards A to rank r+1 in chunks of
+  ``chain_rows`` rows with copy-engine copies into the next rank's landing buffer (no SM touches the bytes), each
+  followed by a flag store; a rank forwards a chunk as soon as its own copy of it has landed, so all links of the
+  chain are busy at once and every hop runs at the unicast NVLink rate.  A step's forwarding is enqueued by one
+  library call; the chunks alternate between ``chain_streams`` streams so that the small kernels around one copy
+  run while the next copy keeps the link busy.  ``chain_fused`` (default) runs ONE gated GEMM launch per step on
+  the receiving ranks, whose loaders wait inside the kernel for the chunk count of their tile's rows; without it
+  there is one launch per row slab, each behind a wait for the chunks that cover the slab.
 * ``nccl``: ``torch.distributed.broadcast`` per slab (any backend; used by the CPU/gloo tests).
   Its wide CTAs cannot share an SM with the GEMM's, so on 8 GPUs transfer and math serialise.
 
@@ -123,8 +124,7 @@ class NShardedGemm:
     def __init__(self, m: int, n: int, k: int, group=None, root: int = 0, slabs: int = 0,
                  gemm_fn: Optional[Callable] = None, device=None, ctx=None, transport: str = "auto",
                  push_ctas: int = 0, mc_stages: int = 1, chain_rows: int = 1024,
-                 chain_in_library: bool = False, chain_fused: bool = False, chain_streams: int = 1,
-                 **plan_args):
+                 chain_fused: bool = True, chain_streams: int = 2, **plan_args):
         import torch
         import torch.distributed as dist
         self.dist = dist
@@ -153,10 +153,9 @@ class NShardedGemm:
         self._a_local = None
         self.push_ctas = push_ctas
         self.chain_rows = max(256, chain_rows // 256 * 256)  # rows of A per forwarded chunk
-        self.chain_in_library = chain_in_library  # enqueue a step's forwarding with one library call
         # one GEMM launch per step whose loaders wait for the rows of A inside the kernel, instead of one per slab
         self.chain_fused = chain_fused
-        if chain_streams != 1 and self.ctx is not None:  # library-enqueued forwarding alternates chunks between two streams
+        if self.ctx is not None:  # the forwarded chunks alternate between this many streams
             self.ctx.set("chain_streams", chain_streams)
         self.mc_stages = mc_stages  # 2: root scatters chunks, every rank multicasts its own; 1: the root multicasts everything
         self.step = 0
@@ -282,10 +281,18 @@ class NShardedGemm:
         self.step += 1
         return c_shard
 
-    def _run_chain(self, a_root, b_shard, c_shard):
+    def _run_chain(self, a_root, b_shard, c_shard, a_ready=None):
         """Rank r receives chunks from r - 1 and forwards them to r + 1 with copy-engine copies; the flag word
         LANDED of a rank counts the chunks that have arrived there.  Ranks are chained in rank order from the root
-        (the root must be rank 0)."""
+        (the root must be rank 0).
+
+        Streams.  The forwarding of a step is enqueued on a helper stream with one library call
+        (``maize_chain_forward``); the GEMM on the caller's stream.  What the helper stream has to wait for before it
+        may read A on the root: ``a_ready`` (a CUDA event after which A is valid) when given, else everything the
+        caller's stream holds so far.  With an event, the replication of step s + 1 runs while step s still
+        multiplies (the landing buffers are double-buffered and a rank's buffer is only overwritten after that rank
+        has acknowledged the step that used it), so that back-to-back steps are bound by the slower of transfer and
+        math instead of their sum.  The receiving ranks' forwarding never depends on their compute stream."""
         import torch
         mc, ctx, G = self._mc, self.ctx, self.world
         if self.root != 0:
@@ -303,21 +310,18 @@ class NShardedGemm:
         last = r == G - 1
         if not last:
             nxt = mc["peer_base"][r + 1]
-            push.wait_stream(cur)  # root: A may come from earlier work; others: orders this step after the last one
+            if r == 0:
+                if a_ready is not None:
+                    push.wait_event(a_ready)
+                else:
+                    push.wait_stream(cur)  # A may come from earlier work of the caller's stream
             if self.step >= 2:
                 # the next rank's buffer of this parity was last used in step - 2
                 ctx.flags_wait(flags_local + self._W_ACK * 4, 1, self.step - 1, stream=push)
             src_base = a_root.data_ptr() if r == 0 else mc["local_base"] + par_off
-            if self.chain_in_library:
-                ctx.chain_forward(None if r == 0 else flags_local + self._W_LANDED * 4, base + 1, nxt + par_off, src_base,
-                                  self.m * row_bytes, self.chain_rows * row_bytes,
-                                  nxt + mc["flags_off"] + self._W_LANDED * 4, stream=push)
-            for i, (lo, hi) in enumerate(chunks if not self.chain_in_library else []):
-                if r != 0:
-                    ctx.flags_wait(flags_local + self._W_LANDED * 4, 1, base + i + 1, stream=push)
-                ctx.copy_async(nxt + par_off + lo * row_bytes, src_base + lo * row_bytes, (hi - lo) * row_bytes,
-                               stream=push)
-                ctx.flag_store(nxt + mc["flags_off"] + self._W_LANDED * 4, base + i + 1, stream=push)
+            ctx.chain_forward(None if r == 0 else flags_local + self._W_LANDED * 4, base + 1, nxt + par_off, src_base,
+                              self.m * row_bytes, self.chain_rows * row_bytes,
+                              nxt + mc["flags_off"] + self._W_LANDED * 4, stream=push)
         a = a_root if r == 0 else self._landing(parity)
         if self.chain_fused:
             if r == 0:
@@ -355,11 +359,14 @@ class NShardedGemm:
                 for r in range(self.world)]
         return torch.cat(cols, dim=1)
 
-    def run(self, a_root, b_shard, c_shard):
-        """One step: replicate A from the root slab by slab and multiply as slabs arrive.
+    def run(self, a_root, b_shard, c_shard, a_ready=None):
+        """One step: replicate A from the root and multiply as its rows arrive.
 
         ``a_root`` is the M x K matrix on the root and ignored elsewhere (may be None);
         ``b_shard`` is this rank's (hi-lo) x K block of B; ``c_shard`` is M x (hi-lo).
+        ``a_ready`` (root, chain transport): a ``torch.cuda.Event`` after which ``a_root`` holds this step's A.
+        Without it the replication waits for everything the current stream holds, the previous step's GEMM
+        included; with it, the replication of a step overlaps the previous step's math.
         """
         if self.world == 1:
             self.gemm_fn(a_root, b_shard, c_shard)
@@ -367,7 +374,7 @@ class NShardedGemm:
         if self.transport == "multimem":
             return self._run_multimem(a_root, b_shard, c_shard)
         if self.transport == "chain":
-            return self._run_chain(a_root, b_shard, c_shard)
+            return self._run_chain(a_root, b_shard, c_shard, a_ready)
         is_root = self.rank == self.root
         a = a_root if is_root else self.a_buffer(b_shard)
         src = self.dist.get_global_rank(self.group, self.root) if self.group is not None else self.root

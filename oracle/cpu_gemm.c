@@ -314,3 +314,16 @@ ORACLE_EXPORT int maize_oracle_num_threads(void)
     return 1;
 #endif
 }
+
+/* Sets the thread count of every later parallel region of this library (fill, check, max-abs and the GEMMs
+ * called with nthreads <= 0).  A launcher may have exported OMP_NUM_THREADS=1 for its children
+ * (torch.distributed.run does); the timed CPU baseline then asks for the cores it may really use. */
+ORACLE_EXPORT void maize_oracle_set_num_threads(int n)
+{
+#ifdef _OPENMP
+    if (n > 0)
+        omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}

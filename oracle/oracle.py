@@ -14,7 +14,7 @@ import numpy as np
 
 __all__ = [
     "build", "lib", "fill_bf16", "gemm_bf16", "gemm_f32out", "gemm_naive", "check",
-    "max_abs_bf16", "num_threads", "bf16_to_f32", "f32_to_bf16", "NORMAL", "UNIFORM",
+    "max_abs_bf16", "num_threads", "set_num_threads", "host_cores", "bf16_to_f32", "f32_to_bf16", "NORMAL", "UNIFORM",
 ]
 
 _HERE = Path(__file__).resolve().parent
@@ -62,6 +62,8 @@ def lib() -> ctypes.CDLL:
         L.maize_oracle_max_abs_bf16.argtypes = [u16p, ctypes.c_uint64]
         L.maize_oracle_max_abs_bf16.restype = ctypes.c_double
         L.maize_oracle_num_threads.restype = ctypes.c_int
+        L.maize_oracle_set_num_threads.argtypes = [ctypes.c_int]
+        L.maize_oracle_set_num_threads.restype = None
         L.maize_oracle_f32_to_bf16.argtypes = [ctypes.c_float]
         L.maize_oracle_f32_to_bf16.restype = ctypes.c_uint16
         L.maize_oracle_bf16_to_f32.argtypes = [ctypes.c_uint16]
@@ -77,6 +79,19 @@ def _u16(a: np.ndarray):
 
 def num_threads() -> int:
     return int(lib().maize_oracle_num_threads())
+
+
+def set_num_threads(n: int) -> None:
+    """Thread count of every later call (overrides an inherited OMP_NUM_THREADS)."""
+    lib().maize_oracle_set_num_threads(int(n))
+
+
+def host_cores() -> int:
+    """Cores this process may run on (its affinity mask), not what OMP_NUM_THREADS says."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
 
 
 def fill_bf16(seed: int, matrix_id: int, shape, dist: int = NORMAL, scale: float = 1.0, first: int = 0) -> np.ndarray:

@@ -37,7 +37,7 @@ def test_bounded_wait_returns_timeout(ctx):
 def test_settings_read_back(ctx):
     """Every key of maize_ctx_set can be read with maize_ctx_get (no kernel is launched here)."""
     for key, value in (("group_rows", 1024), ("pdl", 1), ("b_static", 1), ("push_threads", 256), ("max_ctas", 100),
-                       ("force_kernel", 2), ("debug_flags", 0)):
+                       ("force_kernel", 2), ("debug_flags", 0), ("chain_streams", 2), ("repack_bytes", 4096)):
         before = ctx.get(key)
         try:
             ctx.set(key, value)
@@ -45,6 +45,59 @@ def test_settings_read_back(ctx):
         finally:
             ctx.set(key, before)
     assert ctx.get("sm_count") > 0 and ctx.get("device") == 0 and ctx.get("profile") == 0
+
+
+def test_debug_flags_need_profile(ctx):
+    """The diagnostic switches make results wrong on purpose: they are refused unless profiling is on."""
+    import maize_b200
+    with pytest.raises(maize_b200.MaizeError) as e:
+        ctx.set("debug_flags", 1)
+    assert e.value.status == maize_b200._ffi.INVALID_ARG
+    ctx.set("profile", 1)
+    try:
+        ctx.set("debug_flags", 1)
+        assert ctx.get("debug_flags") == 1
+    finally:
+        ctx.set("profile", 0)
+    assert ctx.get("debug_flags") == 0  # turning profiling off clears them
+
+
+def test_stream_k_recovers_after_a_timeout(ctx, oracle):
+    """A stream-K launch whose waits run out may leave arrival counters half-way (one part of a tile published,
+    another given up).  maize_ctx_poll re-zeroes them when it reports the timeout, so the next launch on the same
+    context is right.  Three CTAs share two tiles of 1024 k-blocks; the budgets below lie around the time one CTA
+    needs for a third and for two thirds of a tile, so that some pieces finish and others give up."""
+    import torch
+    import maize_b200
+    m, n, k = 16, 512, 65536
+    a, b = make_inputs(oracle, m, n, k, 33, scale_b=0.05)
+    da, db = to_device(a), to_device(b)
+    ref = oracle.gemm_bf16(a, b)
+    timed_out = 0
+    for budget_ns in (20_000, 60_000, 120_000, 250_000):
+        ctx.set("force_kernel", 7)
+        ctx.set("max_ctas", 3)
+        ctx.set("timeout_ns", budget_ns)
+        try:
+            junk = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+            ctx.gemm(da, db, out=junk)
+            try:
+                ctx.poll()
+            except maize_b200.MaizeError as e:
+                assert e.status == maize_b200._ffi.TIMEOUT
+                timed_out += 1
+        finally:
+            ctx.set("timeout_ns", 2_000_000_000)
+        try:
+            out = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+            ctx.gemm(da, db, out=out)
+            ctx.poll()
+        finally:
+            ctx.set("max_ctas", 0)
+            ctx.set("force_kernel", 0)
+        assert_parity(oracle, to_host(out), ref, k, oracle.max_abs_bf16(a), oracle.max_abs_bf16(b),
+                      f"after a launch with a {budget_ns} ns budget")
+    assert timed_out >= 1, "no budget was short enough to make a wait run out"
 
 
 @pytest.mark.parametrize("force", [1, 2, 3, 4, 5, 6])
