@@ -69,34 +69,13 @@ __device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity, cons
     }
 }
 
-// Tile order: groups of `group_m` row-blocks sweep all column-blocks, so that the
-// CTAs running at one time share A row panels and B column panels in L2.  This
-// is the grid-stride over (row panel, column panel) pairs of the reference
-// (src/main.rs:56-73, crates/maize_tile/src/gmem/row_panel.rs:95-109) with an
-// L2-aware order.
-struct TileCoord {
-    uint32_t m_blk, n_blk;
-};
-
-__device__ __forceinline__ TileCoord tile_coord(uint32_t t, uint32_t tiles_m, uint32_t tiles_n, uint32_t group_m)
-{
-    const uint32_t per_group = group_m * tiles_n;
-    const uint32_t g = t / per_group;
-    const uint32_t first_m = g * group_m;
-    const uint32_t rows = min(tiles_m - first_m, group_m);
-    const uint32_t r = t - g * per_group;
-    TileCoord c;
-    c.m_blk = first_m + r % rows;
-    c.n_blk = r / rows;
-    return c;
-}
-
 struct GemmParams {
     __nv_bfloat16 *c;
     uint64_t ldc;  // elements
     uint32_t m, n, k;
     uint32_t tiles_m, tiles_n;  // in units of the kernel's tile (per CTA pair for the 2-CTA kernel)
     uint32_t group_m;
+    uint32_t serpentine = 0;  // 1: odd groups of row-blocks sweep the column-blocks backwards
     uint32_t c_vec_ok;  // 1: every C row starts 16-byte aligned (ldc % 8 == 0 and base aligned)
     DeviceStatus *status;
     uint64_t timeout_ns;
@@ -115,6 +94,32 @@ struct GemmParams {
     uint32_t gate_base = 0;
     uint32_t gate_rows = 1;
 };
+
+// Tile order: groups of `group_m` row-blocks sweep all column-blocks, so that the
+// CTAs running at one time share A row panels and B column panels in L2.  With
+// `serpentine` odd groups sweep the column-blocks in descending order, so that a group
+// starts on the column panels of B that the previous group left in L2.  This
+// is the grid-stride over (row panel, column panel) pairs of the reference
+// (src/main.rs:56-73, crates/maize_tile/src/gmem/row_panel.rs:95-109) with an
+// L2-aware order.
+struct TileCoord {
+    uint32_t m_blk, n_blk;
+};
+
+__device__ __forceinline__ TileCoord tile_coord(uint32_t t, const GemmParams &p)
+{
+    const uint32_t per_group = p.group_m * p.tiles_n;
+    const uint32_t g = t / per_group;
+    const uint32_t first_m = g * p.group_m;
+    const uint32_t rows = min(p.tiles_m - first_m, p.group_m);
+    const uint32_t r = t - g * per_group;
+    TileCoord c;
+    c.m_blk = first_m + r % rows;
+    c.n_blk = r / rows;
+    if (p.serpentine && (g & 1u))
+        c.n_blk = p.tiles_n - 1u - c.n_blk;
+    return c;
+}
 
 __device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t *p)
 {

@@ -118,7 +118,7 @@ gemm_bf16_sm100_1cta(const __grid_constant__ CUtensorMap tma_a, const __grid_con
             unsigned long long w_empty = 0;
             int32_t gate_seen = 0;
             for (uint32_t t = blockIdx.x; ok && t < num_tiles; t += gridDim.x) {
-                const TileCoord tc = tile_coord(t, p.tiles_m, p.tiles_n, p.group_m);
+                const TileCoord tc = tile_coord(t, p);
                 const bool hot = (p.debug_flags & 1u) != 0u;
                 const int32_t m0 = hot ? 0 : static_cast<int32_t>(tc.m_blk * kBlockM);
                 const int32_t n0 = hot ? 0 : static_cast<int32_t>(tc.n_blk * BN);
@@ -220,7 +220,7 @@ gemm_bf16_sm100_1cta(const __grid_constant__ CUtensorMap tma_a, const __grid_con
         bool ok = true;
         unsigned long long w_accfull = 0, w_drain = 0, n_tiles_done = 0;
         for (uint32_t t = blockIdx.x; ok && t < num_tiles; t += gridDim.x) {
-            const TileCoord tc = tile_coord(t, p.tiles_m, p.tiles_n, p.group_m);
+            const TileCoord tc = tile_coord(t, p);
             {
                 WaitTimer wt(prof);
                 ok = wait_bounded(acc_full_bar(acc), acc_phase, ctl, 3);

@@ -125,7 +125,7 @@ gemm_bf16_sm100_2cta(const __grid_constant__ CUtensorMap tma_a, const __grid_con
             const uint64_t pol_a = hints ? ptx::policy_evict_last() : ptx::policy_evict_normal();
             const uint64_t pol_b = (p.debug_flags & 8u) ? ptx::policy_evict_first() : ptx::policy_evict_normal();
             for (uint32_t t = pair; ok && t < num_tiles; t += num_pairs) {
-                const TileCoord tc = tile_coord(t, p.tiles_m, p.tiles_n, p.group_m);
+                const TileCoord tc = tile_coord(t, p);
                 const bool hot = (p.debug_flags & 1u) != 0u;
                 const int32_t m0 = static_cast<int32_t>((hot ? 0 : tc.m_blk * kPairBlockM) + cta_rank * kBlockM);
                 const int32_t n0 = static_cast<int32_t>((hot ? 0 : tc.n_blk * BN) + cta_rank * (BN / 2));
@@ -240,7 +240,7 @@ gemm_bf16_sm100_2cta(const __grid_constant__ CUtensorMap tma_a, const __grid_con
         bool ok = true;
         unsigned long long w_accfull = 0, w_drain = 0, n_tiles_done = 0;
         for (uint32_t t = pair; ok && t < num_tiles; t += num_pairs) {
-            const TileCoord tc = tile_coord(t, p.tiles_m, p.tiles_n, p.group_m);
+            const TileCoord tc = tile_coord(t, p);
             {
                 WaitTimer wt(prof);
                 ok = wait_bounded<true>(acc_full_bar(acc), acc_phase, ctl, 3);

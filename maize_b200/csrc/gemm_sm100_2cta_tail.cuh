@@ -135,7 +135,7 @@ gemm_bf16_sm100_2cta_tail(const __grid_constant__ CUtensorMap tma_a, const __gri
             int32_t gate_seen = 0;
             TailWork w;
             for (uint32_t i = 0; ok && tail_work(tp, pair, num_pairs, num_steps, i, w); ++i) {
-                const TileCoord tc = tile_coord(w.tile, p.tiles_m, p.tiles_n, p.group_m);
+                const TileCoord tc = tile_coord(w.tile, p);
                 const int32_t m0 = static_cast<int32_t>(tc.m_blk * kPairBlockM + cta_rank * kBlockM);
                 const int32_t n0 = static_cast<int32_t>(tc.n_blk * BN + cta_rank * (BN / 2));
                 if (!(ok = gate_rows_landed(p, static_cast<uint32_t>(m0) + kBlockM, gate_seen, ctl)))
@@ -218,7 +218,7 @@ gemm_bf16_sm100_2cta_tail(const __grid_constant__ CUtensorMap tma_a, const __gri
         bool ok = true;
         TailWork w;
         for (uint32_t i = 0; ok && tail_work(tp, pair, num_pairs, num_steps, i, w); ++i) {
-            const TileCoord tc = tile_coord(w.tile, p.tiles_m, p.tiles_n, p.group_m);
+            const TileCoord tc = tile_coord(w.tile, p);
             ok = wait_bounded<true>(acc_full_bar(acc), acc_phase, ctl, 3);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok)

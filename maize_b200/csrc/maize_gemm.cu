@@ -100,6 +100,7 @@ struct maize_ctx {
     uint32_t pdl = 0;       // launch the decode kernel with programmatic stream serialization
     uint32_t b_static = 0;  // the caller guarantees that nothing earlier in the stream writes B (weights)
     uint32_t push_threads = 512;  // threads per CTA of the copy kernels of the multi-GPU path
+    uint32_t serpentine = 0;      // odd groups of row-blocks sweep the column-blocks backwards
     uint32_t tma_promotion = 3;   // CUtensorMapL2promotion of the operand maps: 0 none, 1 64 B, 2 128 B, 3 256 B
     uint32_t tail_split = 1;      // split the last partial round of pair tiles along K when pairs would idle
     uint32_t chain_streams = 1;   // 2: maize_chain_forward alternates chunks between the caller's stream and a helper
@@ -514,6 +515,7 @@ maize_status_t gemm_impl(maize_ctx_t *ctx, const void *a, uint64_t lda, const vo
     p.group_m = ctx->group_rows / kv.block_m;  // row-blocks swept together: their rows of A stay hot in L2
     if (p.group_m == 0)
         p.group_m = 1;
+    p.serpentine = ctx->serpentine;
     p.c_vec_ok = (ldc % 8 == 0 && reinterpret_cast<uintptr_t>(c) % 16 == 0) ? 1u : 0u;
     p.status = ctx->d_status;
     p.timeout_ns = ctx->timeout_ns;
@@ -983,6 +985,8 @@ maize_status_t maize_ctx_set(maize_ctx_t *ctx, const char *key, int64_t value)
         if (value < 0 || value > 3)
             return fail(ctx, MAIZE_ERR_INVALID_ARG, "tma_promotion: 0 (none), 1 (64 B), 2 (128 B) or 3 (256 B)");
         ctx->tma_promotion = static_cast<uint32_t>(value);
+    } else if (!strcmp(key, "serpentine")) {
+        ctx->serpentine = value ? 1u : 0u;
     } else if (!strcmp(key, "tail_split")) {
         ctx->tail_split = value ? 1u : 0u;
     } else if (!strcmp(key, "chain_streams")) {
@@ -1038,6 +1042,8 @@ maize_status_t maize_ctx_get(const maize_ctx_t *ctx, const char *key, int64_t *v
         *value = ctx->chain_streams;
     else if (!strcmp(key, "tail_split"))
         *value = ctx->tail_split;
+    else if (!strcmp(key, "serpentine"))
+        *value = ctx->serpentine;
     else if (!strcmp(key, "tma_promotion"))
         *value = ctx->tma_promotion;
     else if (!strcmp(key, "repack_bytes"))
