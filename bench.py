@@ -31,6 +31,10 @@ from pathlib import Path
 
 ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
+# NCCL prints its version banner on stdout at VERSION level; stdout must carry the JSON line only.  Set before
+# anything loads NCCL.
+if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
+    os.environ["NCCL_DEBUG"] = "WARN"
 
 WORKLOADS = {
     # name: (M, N, K, sigma_a, sigma_b, dist, seed, description)
@@ -402,9 +406,6 @@ def main():
     from maize_b200.sharded import NShardedGemm, shard_bounds
     from oracle import oracle
 
-    # NCCL prints its version banner on stdout at VERSION level; stdout must carry the JSON line only
-    if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
-        os.environ["NCCL_DEBUG"] = "WARN"
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
