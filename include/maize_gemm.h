@@ -249,6 +249,55 @@ MAIZE_API maize_status_t maize_flags_wait(maize_ctx_t *ctx, const void *flags, u
 MAIZE_API maize_status_t maize_flag_store(maize_ctx_t *ctx, void *flag, uint32_t value, void *cuda_stream);
 
 /*
+ * The N-sharded multi-GPU GEMM for ONE host process that drives several GPUs of a box.  The reference is
+ * single-GPU; a caller that binds where its GEMM entry point sits (crates/maize_tile/src/gemm/mod.rs:37-55) gets
+ * the split of B's column panels (crates/maize_tile/src/gmem/col_panel.rs:88-124) across GPUs from these.
+ *
+ * maize_mgpu_create: `devices` lists n distinct CUDA device ordinals (1 <= n <= 16) with peer access between
+ * them.  Creates one context, two streams and a small flag buffer per device, enables peer access and starts
+ * one host thread per device (each enqueues its own device's part of a call).
+ *
+ * maize_gemm_bf16_nsharded: C[:, shard g] = A * B[shard g]^T on every device g, A living on device index `root`
+ * before the call.  Shard g = rows [first, end) of B as maize_mgpu_shard reports them (near-equal contiguous
+ * blocks, the larger ones first).  Arrays are indexed like `devices`:
+ *   a_on_root   M x K on device `root`, dense rows
+ *   a_local[g]  M x K landing buffer on device g (entry `root` is ignored and may be NULL)
+ *   b_shards[g] (end - first) x K on device g, dense rows;  c_shards[g]  M x (end - first) on device g, dense rows
+ * A is forwarded along the chain root, root+1, ... (index order, wrapping) in chunks of "chunk_rows" rows with
+ * device-to-device copies; the root runs one GEMM launch, every other device one gated launch
+ * (maize_gemm_bf16_gated).  The call returns when everything is enqueued on the handle's own streams;
+ * maize_mgpu_sync waits for all devices and reports a device-side timeout like maize_ctx_poll.  The buffers of a
+ * call must stay untouched until then, except that the next call may follow at once: it orders itself after the
+ * previous one (a landing buffer is only overwritten after the device that owns it has finished reading it).
+ * By default the forwarding waits for what device `root`'s stream (maize_mgpu_stream) holds when the call is
+ * made, so work that produces A may be enqueued there; maize_mgpu_set("a_on_stream", 0) declares that A is
+ * complete in memory when the call is made, which lets the forwarding of a call overlap the previous call's GEMMs.
+ *
+ * maize_gemm_bf16_nsharded_host: the same from HOST buffers (A M x K, B N x K, C M x N dense): copies A to the
+ * root and each device's rows of B up, runs the sharded GEMM, copies every device's column block into the dense
+ * C and waits.  Device staging is cached in the handle and grows on demand.
+ *
+ * maize_mgpu_set: "chunk_rows" (multiple of 256, default 1024), "a_on_stream" (default 1); any other key is
+ * passed to every device's context (maize_ctx_set).
+ */
+typedef struct maize_mgpu maize_mgpu_t;
+MAIZE_API maize_status_t maize_mgpu_create(int n, const int *devices, maize_mgpu_t **out);
+MAIZE_API void maize_mgpu_destroy(maize_mgpu_t *mg);
+MAIZE_API const char *maize_mgpu_last_error(const maize_mgpu_t *mg);
+MAIZE_API int maize_mgpu_size(const maize_mgpu_t *mg);
+/* The stream (a cudaStream_t) on which device `index`'s GEMMs of this handle run. */
+MAIZE_API void *maize_mgpu_stream(const maize_mgpu_t *mg, int index);
+MAIZE_API maize_status_t maize_mgpu_shard(const maize_mgpu_t *mg, uint32_t n_rows, int index, uint32_t *first,
+                                          uint32_t *end);
+MAIZE_API maize_status_t maize_mgpu_set(maize_mgpu_t *mg, const char *key, int64_t value);
+MAIZE_API maize_status_t maize_gemm_bf16_nsharded(maize_mgpu_t *mg, int root, const void *a_on_root, uint32_t m,
+                                                  uint32_t k, void *const *a_local, const void *const *b_shards,
+                                                  uint32_t n, void *const *c_shards);
+MAIZE_API maize_status_t maize_gemm_bf16_nsharded_host(maize_mgpu_t *mg, int root, const void *a_host, uint32_t m,
+                                                       uint32_t k, const void *b_host, uint32_t n, void *c_host);
+MAIZE_API maize_status_t maize_mgpu_sync(maize_mgpu_t *mg);
+
+/*
  * Self-test of the bounded-wait machinery: launches one CTA that waits on a
  * barrier nothing will ever complete, with a budget of `budget_ns`.  The kernel
  * returns by itself; the following maize_ctx_poll reports MAIZE_ERR_TIMEOUT.

@@ -58,6 +58,17 @@ SYMBOLS = {
     "maize_chain_forward": (_int, [_vp, _vp, _u32, _vp, _vp, _u64, _u64, _vp, _vp]),
     "maize_flags_wait": (_int, [_vp, _vp, _u32, _u32, _vp]),
     "maize_flag_store": (_int, [_vp, _vp, _u32, _vp]),
+    "maize_mgpu_create": (_int, [_int, ctypes.POINTER(_int), ctypes.POINTER(_vp)]),
+    "maize_mgpu_destroy": (None, [_vp]),
+    "maize_mgpu_last_error": (ctypes.c_char_p, [_vp]),
+    "maize_mgpu_size": (_int, [_vp]),
+    "maize_mgpu_stream": (_vp, [_vp, _int]),
+    "maize_mgpu_shard": (_int, [_vp, _u32, _int, ctypes.POINTER(_u32), ctypes.POINTER(_u32)]),
+    "maize_mgpu_set": (_int, [_vp, ctypes.c_char_p, _i64]),
+    "maize_gemm_bf16_nsharded": (_int, [_vp, _int, _vp, _u32, _u32, ctypes.POINTER(_vp), ctypes.POINTER(_vp), _u32,
+                                        ctypes.POINTER(_vp)]),
+    "maize_gemm_bf16_nsharded_host": (_int, [_vp, _int, _vp, _u32, _u32, _vp, _u32, _vp]),
+    "maize_mgpu_sync": (_int, [_vp]),
 }
 
 _lib = None

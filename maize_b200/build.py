@@ -16,7 +16,7 @@ from pathlib import Path
 PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 OUT = PKG / "_lib" / "libmaize_gemm.so"
-SOURCES = [CSRC / "maize_gemm.cu"]
+SOURCES = [CSRC / "maize_gemm.cu", CSRC / "maize_mgpu.cu"]
 DEPENDS = sorted(CSRC.glob("*.cu")) + sorted(CSRC.glob("*.cuh")) + [PKG.parent / "include" / "maize_gemm.h"]
 
 NVCC_FLAGS = [

@@ -56,3 +56,15 @@ def test_parity_through_the_c_program(harness, m, n, k):
     r = _run(harness, m, n, k, 7)
     assert r.returncode == 0, r.stdout + r.stderr
     assert " 0 violation(s)" in r.stdout
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("m,n,k", [(1100, 1300, 520), (2500, 2050, 1032)])
+def test_multi_gpu_parity_through_the_c_program(harness, m, n, k):
+    """maize_gemm_bf16_nsharded_host from plain C on every GPU of the box (up to 4; one GPU degenerates to a plain
+    GEMM), two calls with a different A."""
+    import torch
+    g = max(1, min(torch.cuda.device_count(), 4))
+    r = _run(harness, "--mgpu", g, m, n, k, 11)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert r.stdout.count(" 0 violation(s)") == 2 and f"{g} device(s)" in r.stdout
