@@ -75,6 +75,7 @@ struct GemmParams {
     uint32_t m, n, k;
     uint32_t tiles_m, tiles_n;  // in units of the kernel's tile (per CTA pair for the 2-CTA kernel)
     uint32_t group_m;
+    uint32_t pdl = 0;         // 1: launched with programmatic stream serialization (see the kernels' set-up)
     uint32_t serpentine = 0;  // 1: odd groups of row-blocks sweep the column-blocks backwards
     uint32_t c_vec_ok;  // 1: every C row starts 16-byte aligned (ldc % 8 == 0 and base aligned)
     DeviceStatus *status;
@@ -260,6 +261,9 @@ struct RepackSegment {
 
 __global__ void __launch_bounds__(256) repack_rows_kernel(RepackSegment s0, RepackSegment s1, uint32_t cols16)
 {
+    // a GEMM launched behind this copy with programmatic stream serialization may do its set-up meanwhile (it
+    // waits for this grid to complete before it loads anything)
+    ptx::grid_dependency_launch_dependents();
     // blockIdx.y strides over the rows of both segments, x over the 16-byte columns of a row
     const uint32_t total = s0.rows + s1.rows;
     for (uint32_t r = blockIdx.y; r < total; r += gridDim.y) {

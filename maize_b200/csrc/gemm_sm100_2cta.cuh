@@ -111,6 +111,13 @@ gemm_bf16_sm100_2cta(const __grid_constant__ CUtensorMap tma_a, const __grid_con
     ptx::cluster_wait();
     ptx::tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    if (p.pdl) {
+        // Launched with programmatic stream serialization: the set-up above overlapped the tail of the stream's
+        // previous kernel; nothing below (operand loads, stores to C) may run before that kernel has completed.
+        if (threadIdx.x == 0)
+            ptx::grid_dependency_launch_dependents();  // the next kernel may be scheduled as SMs free up
+        ptx::grid_dependency_wait();
+    }
 
     bool role_ok = true;
     if (warp == 0) {

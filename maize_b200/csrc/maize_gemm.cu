@@ -164,6 +164,24 @@ maize_status_t make_operand_map(maize_ctx_t *ctx, CUtensorMap *map, const void *
     return MAIZE_OK;
 }
 
+// Launch with programmatic stream serialization: the kernel may begin (set-up only; it orders itself with
+// griddepcontrol.wait) while the stream's previous kernel is still draining.
+template <typename Kernel, typename... Args>
+cudaError_t launch_pdl(Kernel kernel, uint32_t grid, uint32_t smem_bytes, cudaStream_t stream, const Args &...args)
+{
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(maize::kNumThreads);
+    cfg.dynamicSmemBytes = smem_bytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, args...);
+}
+
 template <typename Kernel>
 maize_status_t launch_kernel(maize_ctx_t *ctx, int variant_index, Kernel kernel, uint32_t smem_bytes,
                              const CUtensorMap &ta, const CUtensorMap &tb, const GemmParams &p, uint32_t grid,
@@ -176,8 +194,13 @@ maize_status_t launch_kernel(maize_ctx_t *ctx, int variant_index, Kernel kernel,
             return fail_cuda(ctx, "cudaFuncSetAttribute(max dynamic smem)", e);
         attr_done = true;
     }
-    kernel<<<grid, maize::kNumThreads, smem_bytes, stream>>>(ta, tb, p);
-    cudaError_t e = cudaGetLastError();
+    cudaError_t e;
+    if (p.pdl) {
+        e = launch_pdl(kernel, grid, smem_bytes, stream, ta, tb, p);
+    } else {
+        kernel<<<grid, maize::kNumThreads, smem_bytes, stream>>>(ta, tb, p);
+        e = cudaGetLastError();
+    }
     if (e != cudaSuccess)
         return fail_cuda(ctx, "kernel launch", e);
     ctx->launches += 1;
@@ -516,6 +539,7 @@ maize_status_t gemm_impl(maize_ctx_t *ctx, const void *a, uint64_t lda, const vo
     if (p.group_m == 0)
         p.group_m = 1;
     p.serpentine = ctx->serpentine;
+    p.pdl = ctx->pdl;
     p.c_vec_ok = (ldc % 8 == 0 && reinterpret_cast<uintptr_t>(c) % 16 == 0) ? 1u : 0u;
     p.status = ctx->d_status;
     p.timeout_ns = ctx->timeout_ns;
@@ -579,8 +603,13 @@ maize_status_t gemm_impl(maize_ctx_t *ctx, const void *a, uint64_t lda, const vo
                 ctx->attr_set[kPairTail] = true;
             }
             const uint64_t busy = tp.full_rounds > 0 ? pairs : uint64_t(tp.tail_tiles) * tp.split;
-            kernel<<<static_cast<uint32_t>(2 * busy), maize::kNumThreads, smem, stream>>>(ta, tb, tp);
-            cudaError_t el = cudaGetLastError();
+            cudaError_t el;
+            if (tp.g.pdl) {
+                el = launch_pdl(kernel, static_cast<uint32_t>(2 * busy), smem, stream, ta, tb, tp);
+            } else {
+                kernel<<<static_cast<uint32_t>(2 * busy), maize::kNumThreads, smem, stream>>>(ta, tb, tp);
+                el = cudaGetLastError();
+            }
             if (el != cudaSuccess)
                 return fail_cuda(ctx, "kernel launch", el);
             ctx->launches += 1;

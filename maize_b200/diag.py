@@ -14,9 +14,11 @@
            ``--pad`` elements, in the four combinations: tells a slow epilogue (C rows that are not 16-byte
            aligned) from slow loads (operand rows whose pitch is not a multiple of 128 bytes).
 
-Diagnostic flags (``maize_ctx_set("debug_flags", f)``; results are WRONG when set): 1 = every load fetches
-tile (0, 0) so all operand traffic hits in L2, 2 = no loads at all, 4 = A loaded with an evict-last L2 hint,
-8 = B loaded with evict-first (4 and 8: pair kernels only).
+Diagnostic flags (``maize_ctx_set("debug_flags", f)``; results are WRONG when set, and the library takes them
+only while its per-CTA cycle accounting, "profile", is on): 1 = every load fetches tile (0, 0) so all operand
+traffic hits in L2, 2 = no loads at all, 4 = A loaded with an evict-last L2 hint, 8 = B loaded with evict-first
+(4 and 8: pair kernels only).  ``--set key=value`` (repeatable) passes any other tunable to the context, e.g.
+``--set serpentine=1 --set tail_split=0``.
 """
 from __future__ import annotations
 
@@ -42,11 +44,21 @@ def main():
     ap.add_argument("--group-rows", default="2048")
     ap.add_argument("--reps", type=int, default=5)
     ap.add_argument("--pad", default="56,1", help="pitch mode: elements added to lda = ldb and to ldc")
+    ap.add_argument("--set", action="append", default=[], metavar="KEY=VALUE", help="context tunable (repeatable)")
     args = ap.parse_args()
 
     m, n, k = _ints(args.shape)
     torch.cuda.set_device(0)
     ctx = maize_b200.Context(0)
+    for item in args.set:
+        key, value = item.split("=", 1)
+        ctx.set(key, int(value))
+
+    def set_flags(flags):
+        # the library honours the switches only while profiling is on
+        ctx.set("profile", 1 if flags else 0)
+        ctx.set("debug_flags", flags)
+
     a = torch.randn(m, k, device="cuda").bfloat16()
     b = torch.randn(n, k, device="cuda").bfloat16()
     c = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
@@ -64,8 +76,7 @@ def main():
         for kern in _ints(args.kernels):
             for flags in _ints(args.flags):
                 ctx.set("force_kernel", kern)
-                ctx.set("debug_flags", flags)
-                ctx.set("profile", 0)
+                set_flags(flags)
                 timed(3)
                 ms = timed(args.reps)
                 ctx.set("profile", 1)
@@ -119,17 +130,17 @@ def main():
         for g in _ints(args.group_rows):
             for flags in _ints(args.flags):
                 ctx.set("group_rows", g)
-                ctx.set("debug_flags", flags)
+                set_flags(flags)
                 ms = timed(1)
                 print(json.dumps({"group_rows": g, "flags": flags, "ms": round(ms, 4)}), flush=True)
     else:
         ctx.set("force_kernel", args.kernel)
         for flags in _ints(args.flags):
-            ctx.set("debug_flags", flags)
+            set_flags(flags)
             ms = timed(args.reps)
             print(json.dumps({"kernel": ctx.pick_kernel(m, n, k), "flags": flags, "ms_per_launch": round(ms, 4)}),
                   flush=True)
-    ctx.set("debug_flags", 0)
+    set_flags(0)
     ctx.set("force_kernel", 0)
     ctx.poll()
 

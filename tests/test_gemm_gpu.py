@@ -187,6 +187,31 @@ def test_skinny_pair_with_dependent_launch(ctx, oracle):
         assert_parity(oracle, to_host(c), ref, k, 2 * oracle.max_abs_bf16(a), oracle.max_abs_bf16(b), f"launch {i}")
 
 
+@pytest.mark.parametrize("force", [0, 1, 6, 10])
+def test_tiled_kernels_with_dependent_launch(ctx, oracle, force):
+    """"pdl" on the tiled kernels: each launch may start its set-up while the previous kernel drains, and must
+    still see that kernel's output.  A chain of GEMMs where C of one launch is A of the next (several times, back
+    to back, nothing in between) is the case that goes wrong if the dependency wait is missing or misplaced."""
+    import torch
+    m, n, k = 1536, 1024, 1024  # C is m x n, and n == k, so C can be the next A
+    a, b = make_inputs(oracle, m, n, k, 34, scale_b=1.0 / 32)
+    da, db = to_device(a), to_device(b)
+    ctx.set("pdl", 1)
+    ctx.set("force_kernel", force)
+    try:
+        xs = [da]
+        for _ in range(4):
+            xs.append(ctx.gemm(xs[-1], db))
+        ctx.poll()
+    finally:
+        ctx.set("pdl", 0)
+        ctx.set("force_kernel", 0)
+    for i in range(4):
+        x = to_host(xs[i])
+        assert_parity(oracle, to_host(xs[i + 1]), oracle.gemm_bf16(x, b), k, oracle.max_abs_bf16(x), oracle.max_abs_bf16(b),
+                      f"link {i} of the chain, kernel {force}")
+
+
 def test_skinny_pair_rejects_more_than_one_wave(ctx):
     import torch
     import maize_b200
