@@ -139,7 +139,8 @@ MAIZE_API maize_status_t maize_gemm_bf16_kn_ld(maize_ctx_t *ctx, const void *a, 
  * `cuda_stream`, and waits for the result.  Large problems are pipelined: B first,
  * then A in row slabs whose GEMMs and C read-backs overlap the following uploads
  * (two helper streams of the context).  Device staging is cached in the context and
- * grows on demand.
+ * grows on demand.  With "b_static" set, a call that passes the same b_host, b_rows and
+ * b_cols as the previous one re-uses the copy of B that is still on the device.
  * Stands where a host caller of the traced kernel (src/main.rs:31-90) would.
  */
 MAIZE_API maize_status_t maize_gemm_bf16_host(maize_ctx_t *ctx, const void *a_host, uint32_t a_rows, uint32_t a_cols,

@@ -407,6 +407,35 @@ def test_host_entry_point_pipelined(ctx, oracle):
                       "pipelined host entry")
 
 
+@pytest.mark.parametrize("m,n,k", [(300, 520, 264), (5000, 3000, 2048)])
+def test_host_entry_point_keeps_a_static_b_on_the_device(ctx, oracle, m, n, k):
+    """With "b_static" a second call with the same host B re-uses the copy on the device (A changes, B does not
+    cross PCIe again); once the promise is withdrawn a changed B is uploaded again.  Both the single-copy and the
+    pipelined form."""
+    import torch
+    a1, b = make_inputs(oracle, m, n, k, 35)
+    a2 = oracle.fill_bf16(36, 0, (m, k))
+    pa = torch.from_numpy(a1.view(np.int16).copy()).pin_memory()
+    pb = torch.from_numpy(b.view(np.int16).copy()).pin_memory()
+    pc = torch.zeros((m, n), dtype=torch.int16).pin_memory()
+    ma, mb = max(oracle.max_abs_bf16(a1), oracle.max_abs_bf16(a2)), oracle.max_abs_bf16(b)
+    ctx.set("b_static", 1)
+    try:
+        for a in (a1, a2, a1):
+            pa.copy_(torch.from_numpy(a.view(np.int16)))
+            pc.zero_()
+            ctx.gemm_host(pa.data_ptr(), m, k, pb.data_ptr(), n, k, pc.data_ptr(), m, n)
+            ctx.poll()
+            assert_parity(oracle, pc.numpy().view(np.uint16), oracle.gemm_bf16(a, b), k, ma, mb, "static B")
+    finally:
+        ctx.set("b_static", 0)
+    b2 = oracle.fill_bf16(37, 1, (n, k))
+    pb.copy_(torch.from_numpy(b2.view(np.int16)))
+    ctx.gemm_host(pa.data_ptr(), m, k, pb.data_ptr(), n, k, pc.data_ptr(), m, n)
+    ctx.poll()
+    assert_parity(oracle, pc.numpy().view(np.uint16), oracle.gemm_bf16(a1, b2), k, ma, oracle.max_abs_bf16(b2), "new B")
+
+
 @pytest.mark.parametrize("force", [0, 1, 6])
 @pytest.mark.parametrize("name", ["c1", "c2", "c3"])
 def test_baseline_configs_full(ctx, oracle, name, force):
