@@ -19,6 +19,7 @@
 #include "gemm_sm100_2cta_tail.cuh"
 #include "gemm_sm100_skinny.cuh"
 #include "gemm_sm100_skinny_pair.cuh"
+#include "gemm_sm100_skinny_pair_tall.cuh"
 #include "mc_bcast.cuh"
 
 namespace {
@@ -53,12 +54,15 @@ const KernelVariant kVariants[] = {
     {"sm100_skinny_pair_m32_128xNx64_s4", 32, 256, 256, 2},
     // the CTA-pair kernel with the last, partial round of tiles split along K (forced only for now)
     {"sm100_2cta_256x256x128_s3_tail", 256, 256, 128, 2},
+    // the pair-split decode kernel for 32 < M <= 128: A tile loaded once, halves exchanged through the whole ring
+    {"sm100_skinny_pair_m128_128xNx64_s4", 128, 256, 256, 2},
 };
 constexpr int kPairWide = 5;     // index of the CTA-pair kernel with 128-wide stages
 constexpr int kFirstSkinny = 6;  // indices of the skinny variants
 constexpr int kLastSkinny = 7;
 constexpr int kSkinnyPair = 8;
 constexpr int kPairTail = 9;
+constexpr int kSkinnyPairTall = 10;
 constexpr int kNumVariants = static_cast<int>(sizeof(kVariants) / sizeof(kVariants[0]));
 constexpr int kMaxProfileCtas = 1024;
 constexpr int kMaxHostSlabs = 16;  // row slabs of A / C that the host entry point pipelines over PCIe
@@ -255,8 +259,13 @@ int pick_variant(const maize_ctx_t *ctx, uint32_t m, uint32_t n, uint32_t k)
             return kSkinnyPair;
         return kFirstSkinny;
     }
-    if (m <= 128 && (uint64_t(n) + 255) / 256 < 2ull * sms)
+    if (m <= 128 && (uint64_t(n) + 255) / 256 < 2ull * sms) {
+        double pair_us = 0, streamk_us = 0;
+        // the taller exchange (up to 128 KiB through shared memory) costs ~1.5 us more than the M <= 32 one
+        if (skinny_pair_tile(sms, n, k, &pair_us, &streamk_us) != 0 && pair_us + 1.5 <= streamk_us)
+            return kSkinnyPairTall;
         return kFirstSkinny + 1;
+    }
     // A tcgen05.mma costs the same whatever its N, so the tile is as wide as N allows: 32 / 64 / 128 wide only
     // when N itself is that narrow, otherwise 256.  Between one CTA per 128 x 256 tile and a CTA pair per
     // 256 x 256 tile (same work per CTA and per tile time, a third less operand traffic for the pair) the
@@ -358,7 +367,7 @@ maize_status_t gemm_impl(maize_ctx_t *ctx, const void *a, uint64_t lda, const vo
     int vi = pick_variant(ctx, m, n, k);
     if (gate) {
         // only the tiled kernels watch the gate; a forced or chosen decode kernel is replaced
-        if (vi >= kFirstSkinny)
+        if (vi >= kFirstSkinny && vi != kPairTail)
             vi = n > 128 ? 0 : (n > 64 ? 1 : (n > 32 ? 2 : 3));
     }
     if (b_kn) {
@@ -366,7 +375,7 @@ maize_status_t gemm_impl(maize_ctx_t *ctx, const void *a, uint64_t lda, const vo
         if (ctx->force_kernel != 0) {
             if (vi == 3 || vi >= kFirstSkinny)
                 return fail(ctx, MAIZE_ERR_UNSUPPORTED, "this kernel variant does not take a K x N matrix B");
-        } else if (vi >= kFirstSkinny) {
+        } else if (vi >= kFirstSkinny && vi != kPairTail) {
             vi = n > 128 ? 0 : (n > 64 ? 1 : 2);
         } else if (vi == 3) {
             vi = 2;
@@ -374,7 +383,8 @@ maize_status_t gemm_impl(maize_ctx_t *ctx, const void *a, uint64_t lda, const vo
     }
     const KernelVariant &kv = kVariants[vi];
 
-    if (vi == kSkinnyPair) {
+    if (vi == kSkinnyPair || vi == kSkinnyPairTall) {
+        const bool tall = vi == kSkinnyPairTall;
         if (m > kv.block_m)
             return fail(ctx, MAIZE_ERR_UNSUPPORTED, "forced skinny kernel takes fewer rows of A than M");
         double pair_us = 0, streamk_us = 0;
@@ -382,7 +392,7 @@ maize_status_t gemm_impl(maize_ctx_t *ctx, const void *a, uint64_t lda, const vo
         if (bn == 0)
             return fail(ctx, MAIZE_ERR_UNSUPPORTED, "forced pair-split skinny kernel: N needs more than one wave of tiles");
         CUtensorMap tx, tw;
-        maize_status_t sst = make_operand_map(ctx, &tx, a, m, k, lda, 32);
+        maize_status_t sst = make_operand_map(ctx, &tx, a, m, k, lda, tall ? 128 : 32);
         if (sst != MAIZE_OK)
             return sst;
         sst = make_operand_map(ctx, &tw, b, n, k, ldb, bn);
@@ -405,7 +415,7 @@ maize_status_t gemm_impl(maize_ctx_t *ctx, const void *a, uint64_t lda, const vo
         pp.bn = bn;
         pp.tiles_n = (n + bn - 1) / bn;
         pp.num_kb = (k + maize::kBlockK - 1) / maize::kBlockK;
-        auto kernel = maize::gemm_bf16_sm100_skinny_pair<4>;
+        auto kernel = tall ? maize::gemm_bf16_sm100_skinny_pair_tall<4> : maize::gemm_bf16_sm100_skinny_pair<4>;
         if (!ctx->attr_set[vi]) {
             cudaError_t ea = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                   maize::SkinnySmemLayout<4>::kDynamicBytes);

@@ -114,7 +114,8 @@ def test_kernel_selection_table():
     assert pick(4096, 24, 4096) == "sm100_1cta_128x32x64_s8"
     assert pick(16, 16384, 4096) == "sm100_skinny_pair_m32_128xNx64_s4"
     assert pick(16, 300000, 64) == "sm100_skinny_m32_128x256x64_s4"  # more than one wave of pairs: stream-K
-    assert pick(100, 4096, 4096) == "sm100_skinny_m128_128x256x64_s4"
+    assert pick(100, 4096, 4096) == "sm100_skinny_pair_m128_128xNx64_s4"  # one wave of pairs covers N
+    assert pick(100, 40000, 512) == "sm100_skinny_m128_128x256x64_s4"     # it does not: stream-K
 
 
 def _split_args(arglist):

@@ -158,6 +158,30 @@ def test_skinny_pair_split(ctx, oracle, m, n, k):
     run_case(ctx, oracle, m, n, k, seed=28, force=9)
 
 
+@pytest.mark.parametrize("m,n,k", [
+    (128, 16384, 4096), (33, 9472, 64), (100, 4096, 4096), (64, 1000, 520), (77, 18944, 1088), (40, 33, 72),
+    (128, 8191, 136), (96, 16385, 264), (16, 4096, 1024),
+])
+def test_skinny_pair_split_tall(ctx, oracle, m, n, k):
+    """The pair-split decode kernel for 32 < M <= 128 (A tile loaded once, halves exchanged through the leader's
+    whole ring): odd and single k-block counts, tile widths from 32 to 256, ragged last tiles, unaligned C rows,
+    and an M <= 32 shape forced through it."""
+    run_case(ctx, oracle, m, n, k, seed=37, force=11)
+    run_case(ctx, oracle, m, n, k, seed=38, force=11)
+
+
+def test_skinny_pair_tall_is_chosen_and_deterministic(ctx, oracle):
+    import torch
+    m, n, k = 100, 4096, 4096
+    assert "skinny_pair_m128" in ctx.pick_kernel(m, n, k)
+    run_case(ctx, oracle, m, n, k, seed=39)
+    a, b = make_inputs(oracle, m, n, k, 40)
+    da, db = to_device(a), to_device(b)
+    outs = [ctx.gemm(da, db).clone() for _ in range(3)]
+    ctx.poll()
+    assert all(torch.equal(outs[0].view(torch.int16), o.view(torch.int16)) for o in outs[1:])
+
+
 def test_skinny_pair_with_dependent_launch(ctx, oracle):
     """Back-to-back decode launches with programmatic dependent launch: A of launch i+1 is produced by a kernel
     that runs between the GEMMs, so the dependency wait is what keeps the result right; B is declared static."""
