@@ -82,7 +82,9 @@ def parse_args():
     p.add_argument("--b-layout", default="nk", choices=["nk", "kn"],
                    help="nk: B stored N x K (the bench's contract); kn: B stored K x N as the reference demo walks it (N = 1 GPU only)")
     p.add_argument("--no-pdl", action="store_true",
-                   help="c3 only: do not use programmatic dependent launch with static weights for the decode kernel")
+                   help="ordinary launches instead of the library's default programmatic dependent launch")
+    p.add_argument("--b-static", action="store_true",
+                   help="declare B static (weights nothing in the stream writes): the decode kernel then prefetches B early")
     p.add_argument("--no-cpu-baseline", action="store_true")
     p.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (for profiler captures)")
     p.add_argument("--no-others", action="store_true", help="skip the brief runs of the other workloads and of cuBLAS")
@@ -208,7 +210,9 @@ def config_for(args, world: int):
                        "A resident on the root, its readiness given by an event: the replication of step s+1 "
                        "overlaps the math of step s, landing buffers double-buffered") + ")",
            "nccl": "NCCL broadcast per row slab"}[transport]
-    decode_pdl = args.workload == "c3" and not args.no_pdl
+    launch = "ordinary launches" if args.no_pdl else "programmatic dependent launch (the library's default)"
+    if args.b_static:
+        launch += ", B declared static (weights)"
     return {
         "workload": f"{args.workload}: {desc}", "M": m, "N": n, "K": k,
         "layout": "A MxK row-major, B KxN row-major, C MxN bf16" if kn else "A MxK row-major, B NxK K-major, C MxN bf16",
@@ -216,7 +220,7 @@ def config_for(args, world: int):
         "l2": (f"rotating over {n_sets} independent input sets ({n_sets * rank_bytes >> 20} MiB > 4x L2), "
                "back-to-back launches") if small else "inputs exceed L2 (back-to-back launches)",
         "algorithmic_bytes": 2 * (m * k + n * k + m * n),
-        "launch": "programmatic dependent launch, B declared static (weights)" if decode_pdl else "plain",
+        "launch": launch,
     }
 
 
@@ -335,7 +339,7 @@ def draw(shape, sigma, dname, dev, gen):
     return (torch.randn(shape, device=dev, generator=gen) * sigma).to(torch.bfloat16)
 
 
-def brief_workload(ctx, name: str, dev, peaks, sampler, reps: int, pdl: bool = False, cublas: bool = True):
+def brief_workload(ctx, name: str, dev, peaks, sampler, reps: int, b_static: bool = False, cublas: bool = True):
     """One of the other workloads on one GPU: warm up, time `reps` launches (rotating over input sets when the
     inputs fit in L2), the same with torch.matmul, and check sampled rows against the CPU oracle."""
     import torch
@@ -347,8 +351,7 @@ def brief_workload(ctx, name: str, dev, peaks, sampler, reps: int, pdl: bool = F
     n_sets = max(1, -(-4 * L2_BYTES // nbytes)) if nbytes < 2 * L2_BYTES else 1
     sets = [(draw((m, k), sa, dname, dev, gen), draw((n, k), sb, dname, dev, gen),
              torch.empty((m, n), dtype=torch.bfloat16, device=dev)) for _ in range(n_sets)]
-    ctx.set("pdl", 1 if pdl else 0)
-    ctx.set("b_static", 1 if pdl else 0)
+    ctx.set("b_static", 1 if b_static else 0)
     try:
         def ours(i):
             a, b, c = sets[i % n_sets]
@@ -359,10 +362,9 @@ def brief_workload(ctx, name: str, dev, peaks, sampler, reps: int, pdl: bool = F
         ms, w0, w1 = time_loop(ours, total)
         ctx.poll()
     finally:
-        ctx.set("pdl", 0)
         ctx.set("b_static", 0)
     out = {"workload": f"{name}: {desc}", "kernel": ctx.pick_kernel(m, n, k), "ms": ms,
-           "launch": "programmatic dependent launch, B declared static" if pdl else "plain",
+           "launch": "library defaults, B declared static (weights)" if b_static else "library defaults",
            "clocks": sampler.summary(w0, w1) if sampler else None}
     if name == "c3":
         gbs = nbytes / (ms * 1e-3) / 1e9
@@ -428,10 +430,10 @@ def main():
         ctx.set("force_kernel", args.force_kernel)
     if args.repack:
         ctx.set("repack_bytes", (m + ns) * ((k + 63) // 64 * 64) * 2)
-    decode_pdl = args.workload == "c3" and not args.no_pdl
-    if decode_pdl:
-        # decode: B holds weights that nothing in the stream writes, so consecutive launches may overlap
-        ctx.set("pdl", 1)
+    if args.no_pdl:
+        ctx.set("pdl", 0)
+    if args.b_static:
+        # B holds weights that nothing in the stream writes
         ctx.set("b_static", 1)
     gen = torch.Generator(device=dev)
     gen.manual_seed(seed)  # every rank draws the same A; B rows are taken from a per-rank stream
@@ -575,10 +577,10 @@ def main():
         del c_lib
     if world == 1 and not args.no_others and args.workload == "c4" and not kn:
         others = []
-        for name, pdl in (("c1", False), ("c2", False), ("c3", False), ("c3", True), ("c5", False), ("t", False)):
+        for name, static in (("c1", False), ("c2", False), ("c3", False), ("c3", True), ("c5", False), ("t", False)):
             try:
-                others.append(brief_workload(ctx, name, dev, peaks, sampler, reps=max(args.steps, 5), pdl=pdl,
-                                             cublas=not pdl))
+                others.append(brief_workload(ctx, name, dev, peaks, sampler, reps=max(args.steps, 5), b_static=static,
+                                             cublas=not static))
             except Exception as exc:  # report, never hide
                 others.append({"workload": name, "error": repr(exc)})
 
@@ -629,7 +631,7 @@ def main():
                "api": "maize_gemm_bf16_host (C ABI, pinned host buffers)" if world == 1 else
                       "pinned host copies + NShardedGemm.run"}
         ctx.poll()
-        if world == 1 and not decode_pdl:
+        if world == 1 and not args.b_static:
             # the same call with B declared static (weights): B stays on the device between calls, only A goes up
             ctx.set("b_static", 1)
             try:

@@ -158,10 +158,19 @@ MAIZE_API maize_status_t maize_ctx_poll(maize_ctx_t *ctx, void *cuda_stream);
  * see maize_kernel_name), "max_ctas" (cap on the persistent grid, 0 = SM count),
  * "profile" (1 = per-CTA cycle accounting, see maize_ctx_read_profile), "group_rows" (rows of A
  * whose tiles are scheduled together, default 2048), "push_threads" (threads per CTA of the copy
- * kernels of the multi-GPU path, default 512), "pdl" (1 = launch the decode kernel with programmatic
- * stream serialization, so that it may start while the stream's previous kernel drains), "b_static"
- * (1 = the caller guarantees that no earlier work of the stream writes B, e.g. inference weights; with
- * "pdl" the kernel then fetches its first B tiles before waiting for that earlier work), "chain_streams"
+ * kernels of the multi-GPU path, default 512), "pdl" (default 1: the GEMM kernels are launched with
+ * programmatic stream serialization, so that a kernel's set-up (barriers, tensor memory, descriptor
+ * prefetch) runs while the stream's previous kernel drains; the kernel waits for that kernel to complete
+ * before it touches A, B or C, so stream order is kept; 0 = ordinary launches), "b_static" (1 = the
+ * caller guarantees that no earlier work of the stream writes B, e.g. inference weights; with "pdl" the
+ * decode kernel then fetches its first B tiles before waiting for that earlier work, the host-buffer entry
+ * point keeps B on the device between calls, and the pitch-aligning pre-pass keeps its copy of B),
+ * "serpentine" (default 1: every other group of row-blocks sweeps the column-blocks backwards, so that it
+ * starts on the panels of B the previous group left in L2), "tail_split" (default 1: when the last round
+ * of 256 x 256 tiles would leave CTA pairs idle, its tiles are split along K over them), "tma_store"
+ * (default 1: the CTA-pair kernels write C through shared memory and TMA stores when C's rows are 16-byte
+ * aligned), "tma_promotion" (L2 promotion of the operand tensor maps: 0 none, 1 64 B, 2 128 B, 3 256 B
+ * = default), "chain_streams"
  * (1 or 2: streams that maize_chain_forward alternates its chunks between), "repack_bytes" (size of an
  * optional scratch, allocated by this call, into which operands whose row pitch is not a multiple of 128
  * bytes are copied with an aligned pitch ahead of a large GEMM; 0 frees it), "debug_flags"

@@ -29,6 +29,11 @@ constexpr uint32_t kNumEpilogueWarps = 4;
 constexpr uint32_t kStageRowBytes = 80;
 constexpr uint32_t kStageWarpBytes = 32 * kStageRowBytes;
 constexpr uint32_t kStageBytesTotal = kNumEpilogueWarps * kStageWarpBytes;
+// Per-warp staging of the TMA-store epilogue: two buffers of 32 rows x 64 bf16 (128 B, 128-byte swizzle) = 2 x 4 KiB.
+// The ragged epilogue's staging above is carved out of the same area.
+constexpr uint32_t kTmaStoreBufBytes = 32 * 128;
+constexpr uint32_t kTmaStageWarpBytes = 2 * kTmaStoreBufBytes;
+constexpr uint32_t kTmaStageBytesTotal = kNumEpilogueWarps * kTmaStageWarpBytes;
 
 struct WaitCtl {
     volatile int *abort_flag;  // shared memory, CTA-wide
@@ -78,6 +83,7 @@ struct GemmParams {
     uint32_t pdl = 0;         // 1: launched with programmatic stream serialization (see the kernels' set-up)
     uint32_t serpentine = 0;  // 1: odd groups of row-blocks sweep the column-blocks backwards
     uint32_t c_vec_ok;  // 1: every C row starts 16-byte aligned (ldc % 8 == 0 and base aligned)
+    uint32_t c_tma_ok = 0;  // 1: the kernel's C tensor map is valid: full tiles leave through shared memory and TMA stores
     DeviceStatus *status;
     uint64_t timeout_ns;
     // Optional per-CTA cycle accounting (null in normal use): kProfileSlots counters per CTA.
@@ -275,6 +281,65 @@ __global__ void __launch_bounds__(256) repack_rows_kernel(RepackSegment s0, Repa
         for (uint32_t c = blockIdx.x * blockDim.x + threadIdx.x; c < cols16; c += gridDim.x * blockDim.x)
             d[c] = s[c];
     }
+}
+
+// The same drain through shared memory and TMA stores, for a C whose rows are 16-byte aligned (c_tma_ok): per 64
+// columns the warp converts its 32 rows to bf16, writes them as 128-byte rows into one of its two 4 KiB staging
+// buffers in the layout the tensor map's 128-byte swizzle expects (16-byte chunk j of row r sits at chunk
+// j ^ (r & 7)), and one lane hands the 32 x 64 box to the TMA unit, which writes whole 128-byte lines and clips
+// what lies beyond M or N.  The stores are asynchronous: `buf` alternates between the two buffers, and a buffer is
+// rewritten only after the store that last used it has read it.  `stage_u32` = shared-window address of the
+// warp's 8 KiB staging area (1024-byte aligned).  The caller ends with tma_store_drain() before the CTA exits.
+template <uint32_t BN>
+__device__ __forceinline__ void drain_accumulator_tma(const GemmParams &p, const CUtensorMap *tma_c, uint32_t stage_u32,
+                                                      uint32_t tmem_acc, uint32_t quarter, uint32_t lane,
+                                                      uint32_t tile_row0, uint32_t tile_col0, uint32_t &buf)
+{
+    static_assert(BN % 64 == 0, "the TMA-store epilogue works in groups of 64 columns");
+    const uint32_t taddr = tmem_acc + ((quarter * 32u) << 16);
+    const uint32_t row0 = tile_row0 + quarter * 32u;
+    if (row0 >= p.m)
+        return;
+#pragma unroll 1
+    for (uint32_t g = 0; g < BN / 64; ++g) {
+        const uint32_t col0 = tile_col0 + g * 64u;
+        if (col0 >= p.n)
+            break;
+        uint32_t v0[32], v1[32];
+        ptx::tmem_ld_32x32b_x32(taddr + g * 64u, v0);
+        ptx::tmem_ld_32x32b_x32(taddr + g * 64u + 32u, v1);
+        ptx::tmem_ld_wait();
+        if (lane == 0)
+            ptx::bulk_wait_group_read<1>();  // the store before the last one (same buffer) has read its source
+        __syncwarp();
+        const uint32_t base = stage_u32 + buf * kTmaStoreBufBytes;
+        const uint32_t row = base + lane * 128u;
+        const uint32_t sw = lane & 7u;
+#pragma unroll
+        for (uint32_t j = 0; j < 4; ++j) {
+            ptx::st_shared_v4(row + ((j ^ sw) << 4), ptx::pack_bf16x2(v0[8 * j], v0[8 * j + 1]),
+                              ptx::pack_bf16x2(v0[8 * j + 2], v0[8 * j + 3]), ptx::pack_bf16x2(v0[8 * j + 4], v0[8 * j + 5]),
+                              ptx::pack_bf16x2(v0[8 * j + 6], v0[8 * j + 7]));
+            ptx::st_shared_v4(row + (((j + 4u) ^ sw) << 4), ptx::pack_bf16x2(v1[8 * j], v1[8 * j + 1]),
+                              ptx::pack_bf16x2(v1[8 * j + 2], v1[8 * j + 3]), ptx::pack_bf16x2(v1[8 * j + 4], v1[8 * j + 5]),
+                              ptx::pack_bf16x2(v1[8 * j + 6], v1[8 * j + 7]));
+        }
+        ptx::fence_proxy_async_shared();
+        __syncwarp();
+        if (lane == 0) {
+            ptx::tma_store_2d(tma_c, base, static_cast<int32_t>(col0), static_cast<int32_t>(row0));
+            ptx::bulk_commit_group();
+        }
+        buf ^= 1u;
+    }
+}
+
+// Waits until every TMA store this warp issued has been performed (lane 0 issued them).
+__device__ __forceinline__ void tma_store_drain(uint32_t lane)
+{
+    if (lane == 0)
+        ptx::bulk_wait_group<0>();
+    __syncwarp();
 }
 
 // One CTA waits on a barrier that nothing completes; exercises the bounded wait.

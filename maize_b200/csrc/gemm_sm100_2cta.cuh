@@ -36,7 +36,7 @@ struct PairSmemLayout {
     static constexpr uint32_t kStageBytes = KBS * (kABytes + kBBytes);  // [A0..A(KBS-1), B0..B(KBS-1)]
     static constexpr uint32_t kRingBytes = STAGES * kStageBytes;
     static constexpr uint32_t kStagingOffset = kRingBytes;
-    static constexpr uint32_t kBarOffset = kStagingOffset + kStageBytesTotal;
+    static constexpr uint32_t kBarOffset = kStagingOffset + kTmaStageBytesTotal;
     static constexpr uint32_t kNumBars = 2 * STAGES + 4;
     static constexpr uint32_t kTmemSlotOffset = kBarOffset + kNumBars * 8;
     static constexpr uint32_t kAbortOffset = kTmemSlotOffset + 4;
@@ -52,7 +52,7 @@ struct PairSmemLayout {
 template <uint32_t BN, uint32_t KBS, uint32_t STAGES, bool B_KN = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNumThreads, 1)
 gemm_bf16_sm100_2cta(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
-                     const GemmParams p)
+                     const __grid_constant__ CUtensorMap tma_c, const GemmParams p)
 {
     using L = PairSmemLayout<BN, KBS, STAGES>;
     static_assert(BN == 256, "pair tile is 256 x 256");
@@ -91,6 +91,8 @@ gemm_bf16_sm100_2cta(const __grid_constant__ CUtensorMap tma_a, const __grid_con
     if (threadIdx.x == 0) {
         ptx::prefetch_tensormap(&tma_a);
         ptx::prefetch_tensormap(&tma_b);
+        if (p.c_tma_ok)
+            ptx::prefetch_tensormap(&tma_c);
         for (uint32_t s = 0; s < STAGES; ++s) {
             ptx::mbar_init(full_bar(s), 1);   // the leader's producer; bytes of both CTAs
             ptx::mbar_init(empty_bar(s), 1);  // one tcgen05.commit of the leader
@@ -242,7 +244,9 @@ gemm_bf16_sm100_2cta(const __grid_constant__ CUtensorMap tma_a, const __grid_con
     } else {
         // ----------------------------------------------------------- epilogue --
         const uint32_t quarter = warp & 3u;
-        uint8_t *stage_warp = smem_gen + L::kStagingOffset + (warp - 2u) * kStageWarpBytes;
+        uint8_t *stage_warp = smem_gen + L::kStagingOffset + (warp - 2u) * kTmaStageWarpBytes;
+        const uint32_t stage_u32 = smem_base + L::kStagingOffset + (warp - 2u) * kTmaStageWarpBytes;
+        uint32_t store_buf = 0;
         uint32_t acc = 0, acc_phase = 0;
         bool ok = true;
         unsigned long long w_accfull = 0, w_drain = 0, n_tiles_done = 0;
@@ -258,8 +262,12 @@ gemm_bf16_sm100_2cta(const __grid_constant__ CUtensorMap tma_a, const __grid_con
                 break;
             ptx::tcgen05_fence_after();
             WaitTimer dt(prof);
-            drain_accumulator<BN>(p, stage_warp, tmem_base + acc * BN, quarter, lane,
-                                  tc.m_blk * kPairBlockM + cta_rank * kBlockM, tc.n_blk * BN);
+            if (p.c_tma_ok)
+                drain_accumulator_tma<BN>(p, &tma_c, stage_u32, tmem_base + acc * BN, quarter, lane,
+                                          tc.m_blk * kPairBlockM + cta_rank * kBlockM, tc.n_blk * BN, store_buf);
+            else
+                drain_accumulator<BN>(p, stage_warp, tmem_base + acc * BN, quarter, lane,
+                                      tc.m_blk * kPairBlockM + cta_rank * kBlockM, tc.n_blk * BN);
             dt.stop(w_drain);
             ++n_tiles_done;
             ptx::tcgen05_fence_before();
@@ -271,6 +279,8 @@ gemm_bf16_sm100_2cta(const __grid_constant__ CUtensorMap tma_a, const __grid_con
                 acc_phase ^= 1u;
             }
         }
+        if (p.c_tma_ok)
+            tma_store_drain(lane);  // the staging buffers must outlive the stores that read them
         if (prof && warp == 2 && lane == 0) {
             prof_out[kProfEpilogueWaitAccFull] = w_accfull;
             prof_out[kProfEpilogueDrain] = w_drain;

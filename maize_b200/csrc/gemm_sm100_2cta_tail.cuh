@@ -72,7 +72,7 @@ __device__ __forceinline__ unsigned int tail_ld_acquire_gpu(const unsigned int *
 template <uint32_t KBS, uint32_t STAGES>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNumThreads, 1)
 gemm_bf16_sm100_2cta_tail(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
-                          const TailParams tp)
+                          const __grid_constant__ CUtensorMap tma_c, const TailParams tp)
 {
     constexpr uint32_t BN = 256;
     using L = PairSmemLayout<BN, KBS, STAGES>;
@@ -104,6 +104,8 @@ gemm_bf16_sm100_2cta_tail(const __grid_constant__ CUtensorMap tma_a, const __gri
     if (threadIdx.x == 0) {
         ptx::prefetch_tensormap(&tma_a);
         ptx::prefetch_tensormap(&tma_b);
+        if (p.c_tma_ok)
+            ptx::prefetch_tensormap(&tma_c);
         for (uint32_t s = 0; s < STAGES; ++s) {
             ptx::mbar_init(full_bar(s), 1);
             ptx::mbar_init(empty_bar(s), 1);
@@ -220,7 +222,9 @@ gemm_bf16_sm100_2cta_tail(const __grid_constant__ CUtensorMap tma_a, const __gri
     } else {
         // ----------------------------------------------------------- epilogue --
         const uint32_t quarter = warp & 3u;
-        uint8_t *stage_warp = smem_gen + L::kStagingOffset + (warp - 2u) * kStageWarpBytes;
+        uint8_t *stage_warp = smem_gen + L::kStagingOffset + (warp - 2u) * kTmaStageWarpBytes;
+        const uint32_t stage_u32 = smem_base + L::kStagingOffset + (warp - 2u) * kTmaStageWarpBytes;
+        uint32_t store_buf = 0;
         uint32_t acc = 0, acc_phase = 0;
         bool ok = true;
         TailWork w;
@@ -233,9 +237,14 @@ gemm_bf16_sm100_2cta_tail(const __grid_constant__ CUtensorMap tma_a, const __gri
             ptx::tcgen05_fence_after();
             const uint32_t tile_row0 = tc.m_blk * kPairBlockM + cta_rank * kBlockM;
             const uint32_t tile_col0 = tc.n_blk * BN;
-            if (w.parts == 1) {
+            if (w.parts == 1 && p.c_tma_ok) {
+                drain_accumulator_tma<BN>(p, &tma_c, stage_u32, tmem_base + acc * BN, quarter, lane, tile_row0, tile_col0,
+                                          store_buf);
+            } else if (w.parts == 1) {
                 drain_accumulator<BN>(p, stage_warp, tmem_base + acc * BN, quarter, lane, tile_row0, tile_col0);
             } else {
+                if (p.c_tma_ok)
+                    tma_store_drain(lane);  // the combining path below re-uses the staging area
                 // slot of (tile of the last round, part, this CTA's half): [column][row] so that a warp's 32 lanes
                 // (= rows) touch 32 consecutive floats
                 const uint32_t taddr = tmem_base + acc * BN + ((quarter * 32u) << 16);
@@ -304,6 +313,8 @@ gemm_bf16_sm100_2cta_tail(const __grid_constant__ CUtensorMap tma_a, const __gri
                 acc_phase ^= 1u;
             }
         }
+        if (p.c_tma_ok)
+            tma_store_drain(lane);  // the staging buffers must outlive the stores that read them
         role_ok = ok;
     }
     if (!role_ok) {

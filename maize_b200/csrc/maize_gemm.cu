@@ -101,10 +101,11 @@ struct maize_ctx {
     int max_ctas = 0;
     uint32_t debug_flags = 0;
     uint32_t group_rows = 2048;
-    uint32_t pdl = 0;       // launch the decode kernel with programmatic stream serialization
+    uint32_t pdl = 1;       // launch the GEMM kernels with programmatic stream serialization
     uint32_t b_static = 0;  // the caller guarantees that nothing earlier in the stream writes B (weights)
     uint32_t push_threads = 512;  // threads per CTA of the copy kernels of the multi-GPU path
-    uint32_t serpentine = 0;      // odd groups of row-blocks sweep the column-blocks backwards
+    uint32_t tma_store = 1;       // pair kernels: C through shared memory and TMA stores when its rows are 16-byte aligned
+    uint32_t serpentine = 1;      // odd groups of row-blocks sweep the column-blocks backwards
     uint32_t tma_promotion = 3;   // CUtensorMapL2promotion of the operand maps: 0 none, 1 64 B, 2 128 B, 3 256 B
     uint32_t tail_split = 1;      // split the last partial round of pair tiles along K when pairs would idle
     uint32_t chain_streams = 1;   // 2: maize_chain_forward alternates chunks between the caller's stream and a helper
@@ -174,6 +175,19 @@ maize_status_t make_operand_map(maize_ctx_t *ctx, CUtensorMap *map, const void *
 
 // Launch with programmatic stream serialization: the kernel may begin (set-up only; it orders itself with
 // griddepcontrol.wait) while the stream's previous kernel is still draining.
+// 2-D bf16 tensor map over C (row-major [rows x cols], row pitch `ld` elements, a multiple of 8) for the TMA-store
+// epilogue: box = [32 rows x 64 elements], 128-byte swizzle.  False if the driver refuses the shape.
+bool make_store_map(maize_ctx_t *ctx, CUtensorMap *map, void *base, uint64_t rows, uint64_t cols, uint64_t ld)
+{
+    cuuint64_t gdim[2] = {cols, rows};
+    cuuint64_t gstride[1] = {ld * 2};
+    cuuint32_t box[2] = {64, 32};
+    cuuint32_t estride[2] = {1, 1};
+    return ctx->encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base, gdim, gstride, box, estride,
+                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 template <typename Kernel, typename... Args>
 cudaError_t launch_pdl(Kernel kernel, uint32_t grid, uint32_t smem_bytes, cudaStream_t stream, const Args &...args)
 {
@@ -190,10 +204,11 @@ cudaError_t launch_pdl(Kernel kernel, uint32_t grid, uint32_t smem_bytes, cudaSt
     return cudaLaunchKernelEx(&cfg, kernel, args...);
 }
 
-template <typename Kernel>
-maize_status_t launch_kernel(maize_ctx_t *ctx, int variant_index, Kernel kernel, uint32_t smem_bytes,
-                             const CUtensorMap &ta, const CUtensorMap &tb, const GemmParams &p, uint32_t grid,
-                             cudaStream_t stream, bool b_kn = false)
+// `args...` = the kernel's arguments: (A map, B map, params) for the one-CTA kernels, (A map, B map, C map, params)
+// for the CTA-pair kernels.
+template <typename Kernel, typename... Args>
+maize_status_t launch_kernel(maize_ctx_t *ctx, int variant_index, Kernel kernel, uint32_t smem_bytes, uint32_t grid,
+                             cudaStream_t stream, bool b_kn, bool pdl, const Args &...args)
 {
     bool &attr_done = b_kn ? ctx->attr_set_kn[variant_index] : ctx->attr_set[variant_index];
     if (!attr_done) {
@@ -203,10 +218,10 @@ maize_status_t launch_kernel(maize_ctx_t *ctx, int variant_index, Kernel kernel,
         attr_done = true;
     }
     cudaError_t e;
-    if (p.pdl) {
-        e = launch_pdl(kernel, grid, smem_bytes, stream, ta, tb, p);
+    if (pdl) {
+        e = launch_pdl(kernel, grid, smem_bytes, stream, args...);
     } else {
-        kernel<<<grid, maize::kNumThreads, smem_bytes, stream>>>(ta, tb, p);
+        kernel<<<grid, maize::kNumThreads, smem_bytes, stream>>>(args...);
         e = cudaGetLastError();
     }
     if (e != cudaSuccess)
@@ -220,7 +235,7 @@ maize_status_t launch_variant(maize_ctx_t *ctx, int variant_index, const CUtenso
                               const GemmParams &p, uint32_t grid, cudaStream_t stream)
 {
     return launch_kernel(ctx, variant_index, maize::gemm_bf16_sm100_1cta<BN, STAGES, B_KN>,
-                         maize::GemmSmemLayout<BN, STAGES>::kDynamicBytes, ta, tb, p, grid, stream, B_KN);
+                         maize::GemmSmemLayout<BN, STAGES>::kDynamicBytes, grid, stream, B_KN, p.pdl != 0, ta, tb, p);
 }
 
 // Tile width for the pair-split skinny kernel: the narrowest multiple of 32 for which one pair per tile
@@ -541,6 +556,13 @@ maize_status_t gemm_impl(maize_ctx_t *ctx, const void *a, uint64_t lda, const vo
     if (st != MAIZE_OK)
         return st;
 
+    // C leaves the pair kernels through shared memory and TMA stores when its rows are 16-byte aligned
+    CUtensorMap tc;
+    memset(&tc, 0, sizeof tc);
+    const bool c_rows_aligned = ldc % 8 == 0 && reinterpret_cast<uintptr_t>(c) % 16 == 0;
+    const bool c_tma = ctx->tma_store && c_rows_aligned && kv.ctas_per_tile == 2 && ldc * 2 < (1ull << 40) &&
+                       make_store_map(ctx, &tc, c, m, n, ldc);
+
     GemmParams p;
     p.c = static_cast<__nv_bfloat16 *>(c);
     p.ldc = ldc;
@@ -554,6 +576,7 @@ maize_status_t gemm_impl(maize_ctx_t *ctx, const void *a, uint64_t lda, const vo
         p.group_m = 1;
     p.serpentine = ctx->serpentine;
     p.pdl = ctx->pdl;
+    p.c_tma_ok = c_tma ? 1u : 0u;
     p.c_vec_ok = (ldc % 8 == 0 && reinterpret_cast<uintptr_t>(c) % 16 == 0) ? 1u : 0u;
     p.status = ctx->d_status;
     p.timeout_ns = ctx->timeout_ns;
@@ -619,9 +642,9 @@ maize_status_t gemm_impl(maize_ctx_t *ctx, const void *a, uint64_t lda, const vo
             const uint64_t busy = tp.full_rounds > 0 ? pairs : uint64_t(tp.tail_tiles) * tp.split;
             cudaError_t el;
             if (tp.g.pdl) {
-                el = launch_pdl(kernel, static_cast<uint32_t>(2 * busy), smem, stream, ta, tb, tp);
+                el = launch_pdl(kernel, static_cast<uint32_t>(2 * busy), smem, stream, ta, tb, tc, tp);
             } else {
-                kernel<<<static_cast<uint32_t>(2 * busy), maize::kNumThreads, smem, stream>>>(ta, tb, tp);
+                kernel<<<static_cast<uint32_t>(2 * busy), maize::kNumThreads, smem, stream>>>(ta, tb, tc, tp);
                 el = cudaGetLastError();
             }
             if (el != cudaSuccess)
@@ -637,10 +660,10 @@ maize_status_t gemm_impl(maize_ctx_t *ctx, const void *a, uint64_t lda, const vo
         case 2: return launch_variant<64, 8, true>(ctx, vi, ta, tb, p, grid, stream);
         case 4:
             return launch_kernel(ctx, vi, maize::gemm_bf16_sm100_2cta<256, 1, 6, true>,
-                                 maize::PairSmemLayout<256, 1, 6>::kDynamicBytes, ta, tb, p, grid, stream, true);
+                                 maize::PairSmemLayout<256, 1, 6>::kDynamicBytes, grid, stream, true, p.pdl != 0, ta, tb, tc, p);
         default:
             return launch_kernel(ctx, vi, maize::gemm_bf16_sm100_2cta<256, 2, 3, true>,
-                                 maize::PairSmemLayout<256, 2, 3>::kDynamicBytes, ta, tb, p, grid, stream, true);
+                                 maize::PairSmemLayout<256, 2, 3>::kDynamicBytes, grid, stream, true, p.pdl != 0, ta, tb, tc, p);
         }
     }
     switch (vi) {
@@ -650,10 +673,10 @@ maize_status_t gemm_impl(maize_ctx_t *ctx, const void *a, uint64_t lda, const vo
     case 3: return launch_variant<32, 8>(ctx, vi, ta, tb, p, grid, stream);
     case 4:
         return launch_kernel(ctx, vi, maize::gemm_bf16_sm100_2cta<256, 1, 6>,
-                             maize::PairSmemLayout<256, 1, 6>::kDynamicBytes, ta, tb, p, grid, stream);
+                             maize::PairSmemLayout<256, 1, 6>::kDynamicBytes, grid, stream, false, p.pdl != 0, ta, tb, tc, p);
     default:
         return launch_kernel(ctx, vi, maize::gemm_bf16_sm100_2cta<256, 2, 3>,
-                             maize::PairSmemLayout<256, 2, 3>::kDynamicBytes, ta, tb, p, grid, stream);
+                             maize::PairSmemLayout<256, 2, 3>::kDynamicBytes, grid, stream, false, p.pdl != 0, ta, tb, tc, p);
     }
 }
 
@@ -1038,6 +1061,8 @@ maize_status_t maize_ctx_set(maize_ctx_t *ctx, const char *key, int64_t value)
         if (value < 0 || value > 3)
             return fail(ctx, MAIZE_ERR_INVALID_ARG, "tma_promotion: 0 (none), 1 (64 B), 2 (128 B) or 3 (256 B)");
         ctx->tma_promotion = static_cast<uint32_t>(value);
+    } else if (!strcmp(key, "tma_store")) {
+        ctx->tma_store = value ? 1u : 0u;
     } else if (!strcmp(key, "serpentine")) {
         ctx->serpentine = value ? 1u : 0u;
     } else if (!strcmp(key, "tail_split")) {
@@ -1097,6 +1122,8 @@ maize_status_t maize_ctx_get(const maize_ctx_t *ctx, const char *key, int64_t *v
         *value = ctx->tail_split;
     else if (!strcmp(key, "serpentine"))
         *value = ctx->serpentine;
+    else if (!strcmp(key, "tma_store"))
+        *value = ctx->tma_store;
     else if (!strcmp(key, "tma_promotion"))
         *value = ctx->tma_promotion;
     else if (!strcmp(key, "repack_bytes"))

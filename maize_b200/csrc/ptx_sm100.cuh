@@ -143,6 +143,44 @@ __device__ __forceinline__ void tma_load_2d_pair_hint(uint32_t smem_dst, const C
         : "memory");
 }
 
+// 2-D tiled store shared memory -> global (the box of the tensor map, swizzled as the map says); elements outside
+// the tensor are not written.  x * 2 bytes must be a multiple of 16 and no coordinate negative.  Completion is
+// tracked by bulk groups of the issuing thread.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, uint32_t smem_src, int32_t x, int32_t y)
+{
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
+                     reinterpret_cast<uint64_t>(map)),
+                 "r"(smem_src), "r"(x), "r"(y)
+                 : "memory");
+}
+
+__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+
+// Until at most N of this thread's bulk groups are still READING their shared-memory source.
+template <int N>
+__device__ __forceinline__ void bulk_wait_group_read()
+{
+    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+
+// Until at most N of this thread's bulk groups are still pending at all (their writes are then performed).
+template <int N>
+__device__ __forceinline__ void bulk_wait_group()
+{
+    asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// Orders this thread's earlier generic-proxy writes to shared memory before later async-proxy (TMA) reads of it.
+__device__ __forceinline__ void fence_proxy_async_shared()
+{
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d)
+{
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+
 // Arrive (release, cluster scope) on a barrier named by a shared::cluster address.
 __device__ __forceinline__ void mbar_arrive_cluster_addr(uint32_t bar_cluster_addr)
 {

@@ -36,8 +36,9 @@ def test_bounded_wait_returns_timeout(ctx):
 
 def test_settings_read_back(ctx):
     """Every key of maize_ctx_set can be read with maize_ctx_get (no kernel is launched here)."""
-    for key, value in (("group_rows", 1024), ("pdl", 1), ("b_static", 1), ("push_threads", 256), ("max_ctas", 100),
-                       ("force_kernel", 2), ("debug_flags", 0), ("chain_streams", 2), ("repack_bytes", 4096)):
+    for key, value in (("group_rows", 1024), ("b_static", 1), ("push_threads", 256), ("max_ctas", 100),
+                       ("force_kernel", 2), ("debug_flags", 0), ("chain_streams", 2), ("repack_bytes", 4096), ("pdl", 0),
+                       ("serpentine", 0), ("tail_split", 0), ("tma_store", 0), ("tma_promotion", 2)):
         before = ctx.get(key)
         try:
             ctx.set(key, value)
@@ -204,15 +205,16 @@ def test_skinny_pair_with_dependent_launch(ctx, oracle):
             x = da * 2 if i % 2 == 0 else da.clone()  # the next launch's A comes from a kernel in between
         ctx.poll()
     finally:
-        ctx.set("pdl", 0)
+        ctx.set("pdl", 1)  # the library's default
         ctx.set("b_static", 0)
     for i, c in enumerate(outs):
         ref = ref1 if i % 2 == 0 else ref2
         assert_parity(oracle, to_host(c), ref, k, 2 * oracle.max_abs_bf16(a), oracle.max_abs_bf16(b), f"launch {i}")
 
 
+@pytest.mark.parametrize("pdl", [1, 0])
 @pytest.mark.parametrize("force", [0, 1, 6, 10])
-def test_tiled_kernels_with_dependent_launch(ctx, oracle, force):
+def test_tiled_kernels_with_dependent_launch(ctx, oracle, force, pdl):
     """"pdl" on the tiled kernels: each launch may start its set-up while the previous kernel drains, and must
     still see that kernel's output.  A chain of GEMMs where C of one launch is A of the next (several times, back
     to back, nothing in between) is the case that goes wrong if the dependency wait is missing or misplaced."""
@@ -220,7 +222,7 @@ def test_tiled_kernels_with_dependent_launch(ctx, oracle, force):
     m, n, k = 1536, 1024, 1024  # C is m x n, and n == k, so C can be the next A
     a, b = make_inputs(oracle, m, n, k, 34, scale_b=1.0 / 32)
     da, db = to_device(a), to_device(b)
-    ctx.set("pdl", 1)
+    ctx.set("pdl", pdl)  # 1 is the default; 0 = ordinary launches
     ctx.set("force_kernel", force)
     try:
         xs = [da]
@@ -228,7 +230,7 @@ def test_tiled_kernels_with_dependent_launch(ctx, oracle, force):
             xs.append(ctx.gemm(xs[-1], db))
         ctx.poll()
     finally:
-        ctx.set("pdl", 0)
+        ctx.set("pdl", 1)  # the library's default
         ctx.set("force_kernel", 0)
     for i in range(4):
         x = to_host(xs[i])
@@ -331,6 +333,36 @@ def test_canaries_around_c(ctx, oracle):
     assert np.all(body[:, n:] == seven)
     assert_parity(oracle, np.ascontiguousarray(body[:, :n]), oracle.gemm_bf16(a, b), k, oracle.max_abs_bf16(a),
                   oracle.max_abs_bf16(b), "strided C")
+
+
+@pytest.mark.parametrize("force", [5, 6, 10])
+@pytest.mark.parametrize("tma_store", [1, 0])
+def test_canaries_around_c_with_aligned_rows(ctx, oracle, force, tma_store):
+    """C rows 16-byte aligned (ldc % 8 == 0) but narrower than the pitch and with ragged M and N: the pair kernels
+    write such a C through shared memory and TMA stores, which must clip at M and N exactly; the direct-store
+    path ("tma_store" = 0) is held to the same."""
+    import torch
+    m, n, k, ldc = 300, 328, 200, 336
+    a, b = make_inputs(oracle, m, n, k, 41)
+    da, db = to_device(a), to_device(b)
+    guard = 1024
+    buf = torch.full((guard + m * ldc + guard,), 7.0, dtype=torch.bfloat16, device="cuda")
+    c_ptr = buf.data_ptr() + guard * 2
+    ctx.set("force_kernel", force)
+    ctx.set("tma_store", tma_store)
+    try:
+        ctx.gemm_ld(da.data_ptr(), k, db.data_ptr(), k, c_ptr, ldc, m, n, k)
+        ctx.poll()
+    finally:
+        ctx.set("force_kernel", 0)
+        ctx.set("tma_store", 1)
+    host = to_host(buf)
+    seven = to_host(torch.full((1,), 7.0, dtype=torch.bfloat16))[0]
+    assert np.all(host[:guard] == seven) and np.all(host[guard + m * ldc:] == seven)
+    body = host[guard:guard + m * ldc].reshape(m, ldc)
+    assert np.all(body[:, n:] == seven)
+    assert_parity(oracle, np.ascontiguousarray(body[:, :n]), oracle.gemm_bf16(a, b), k, oracle.max_abs_bf16(a),
+                  oracle.max_abs_bf16(b), f"aligned strided C, kernel {force}, tma_store {tma_store}")
 
 
 def test_strided_operands(ctx, oracle):
