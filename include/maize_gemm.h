@@ -176,6 +176,8 @@ MAIZE_API maize_status_t maize_ctx_poll(maize_ctx_t *ctx, void *cuda_stream);
  * bytes are copied with an aligned pitch ahead of a large GEMM; 0 frees it), "debug_flags"
  * (performance diagnostics that make results WRONG: 1 = all loads hit one tile, 2 = no loads; refused
  * unless "profile" is 1, cleared when "profile" returns to 0). */
+/* An environment variable MAIZE_<KEY> (upper case, e.g. MAIZE_PDL=0, MAIZE_TMA_STORE=0) presets that tunable in
+ * every context created afterwards; maize_ctx_set still overrides it. */
 MAIZE_API maize_status_t maize_ctx_set(maize_ctx_t *ctx, const char *key, int64_t value);
 /* Reads back any key of maize_ctx_set, plus "sm_count" and "device". */
 MAIZE_API maize_status_t maize_ctx_get(const maize_ctx_t *ctx, const char *key, int64_t *value);

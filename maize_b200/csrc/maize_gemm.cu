@@ -10,6 +10,7 @@
 #include <cuda_runtime.h>
 
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <string>
@@ -750,6 +751,23 @@ maize_status_t maize_ctx_create(int device, maize_ctx_t **out)
         return MAIZE_ERR_CUDA;
     }
     ctx->repack_bytes = kDefaultRepackBytes;
+    // MAIZE_<KEY>=<integer> in the environment presets a tunable of every context (same keys as maize_ctx_set)
+    static const char *const kEnvKeys[] = {"pdl", "tma_store", "serpentine", "tail_split", "group_rows", "tma_promotion",
+                                           "chain_streams", "b_static", "timeout_ns", "max_ctas"};
+    for (const char *key : kEnvKeys) {
+        std::string name = "MAIZE_";
+        for (const char *c = key; *c; ++c)
+            name += static_cast<char>(*c >= 'a' && *c <= 'z' ? *c - 32 : *c);
+        const char *text = getenv(name.c_str());
+        if (text && *text) {
+            char *end = nullptr;
+            const long long v = strtoll(text, &end, 10);
+            if (end && *end == '\0' && maize_ctx_set(ctx, key, v) != MAIZE_OK) {
+                maize_ctx_destroy(ctx);
+                return MAIZE_ERR_INVALID_ARG;
+            }
+        }
+    }
     *out = ctx;
     return MAIZE_OK;
 }
