@@ -70,13 +70,14 @@ def parse_args():
                    help="how A reaches the other GPUs at N > 1 (auto: the copy-engine chain where symmetric memory is available, else nccl)")
     p.add_argument("--mc-stages", type=int, default=1, choices=[1, 2],
                    help="multimem transport: 2 = root scatters chunks and every GPU multicasts its own, 1 = root multicasts all")
-    p.add_argument("--chain-rows", type=int, default=1024, help="chain transport: rows of A per forwarded chunk")
+    p.add_argument("--chain-rows", type=int, default=2048, help="chain transport: rows of A per forwarded chunk")
     p.add_argument("--chain-streams", type=int, default=2, choices=[1, 2],
                    help="chain transport: streams the forwarded chunks alternate between")
     p.add_argument("--chain-fused", type=int, default=1, choices=[0, 1],
                    help="chain transport: 1 = one gated GEMM launch per step (waits for rows inside the kernel), 0 = one per slab")
-    p.add_argument("--serial-steps", action="store_true",
-                   help="N > 1: the replication of a step waits for the previous step's GEMM on the root (no overlap across steps)")
+    p.add_argument("--overlap-steps", action="store_true",
+                   help="N > 1: give the root an event for \"A is ready\" instead of stream order, so that the replication of a "
+                        "step may start while the previous step's GEMM still runs on the root (measured: no difference on 8 GPUs)")
     p.add_argument("--push-ctas", type=int, default=0, help="CTAs of the multicast push kernel (0 = library default)")
     p.add_argument("--e2e-steps", type=int, default=3)
     p.add_argument("--b-layout", default="nk", choices=["nk", "kn"],
@@ -206,9 +207,10 @@ def config_for(args, world: int):
     how = {"multimem": "NVSwitch multicast (multimem.st push kernel)",
            "chain": f"a copy-engine chain (rank r forwards to r+1 in {args.chain_rows}-row chunks over {args.chain_streams} "
                     f"stream(s); {'one gated GEMM launch per step' if args.chain_fused else 'one GEMM launch per row slab'}; "
-                    + ("replication of a step waits for the previous step's GEMM" if args.serial_steps else
-                       "A resident on the root, its readiness given by an event: the replication of step s+1 "
-                       "overlaps the math of step s, landing buffers double-buffered") + ")",
+                    + ("A resident on the root, its readiness given by an event: the replication of step s+1 may start "
+                       "while step s still multiplies on the root" if args.overlap_steps else
+                       "the replication of a step follows the root's previous GEMM in stream order") +
+                    "; landing buffers double-buffered across steps)",
            "nccl": "NCCL broadcast per row slab"}[transport]
     launch = "ordinary launches" if args.no_pdl else "programmatic dependent launch (the library's default)"
     if args.b_static:
@@ -457,10 +459,10 @@ def main():
     op = NShardedGemm(m, n, k, slabs=args.slabs, ctx=ctx, device=dev, transport=args.transport,
                       push_ctas=args.push_ctas, mc_stages=args.mc_stages, gemm_fn=gemm_call if kn else None,
                       chain_rows=args.chain_rows, chain_streams=args.chain_streams, chain_fused=bool(args.chain_fused))
-    # A is resident on the root before the timed region (as `value` is defined); its readiness is an event
-    # recorded once here, so that the replication of a step need not wait for the previous step's GEMM
+    # --overlap-steps: A is resident on the root before the timed region (as `value` is defined); its readiness is
+    # an event recorded once here, so that the replication of a step need not wait for the previous step's GEMM
     a_ready = None
-    if world > 1 and rank == 0 and not args.serial_steps:
+    if world > 1 and rank == 0 and args.overlap_steps:
         a_ready = torch.cuda.Event()
         a_ready.record()
     step_no = [0]

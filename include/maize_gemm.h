@@ -171,7 +171,7 @@ MAIZE_API maize_status_t maize_ctx_poll(maize_ctx_t *ctx, void *cuda_stream);
  * (default 1: the CTA-pair kernels write C through shared memory and TMA stores when C's rows are 16-byte
  * aligned), "tma_promotion" (L2 promotion of the operand tensor maps: 0 none, 1 64 B, 2 128 B, 3 256 B
  * = default), "chain_streams"
- * (1 or 2: streams that maize_chain_forward alternates its chunks between), "repack_bytes" (size of an
+ * (1 or 2 = default: streams that maize_chain_forward alternates its chunks between), "repack_bytes" (size of an
  * optional scratch, allocated by this call, into which operands whose row pitch is not a multiple of 128
  * bytes are copied with an aligned pitch ahead of a large GEMM; 0 frees it), "debug_flags"
  * (performance diagnostics that make results WRONG: 1 = all loads hit one tile, 2 = no loads; refused
@@ -289,7 +289,7 @@ MAIZE_API maize_status_t maize_flag_store(maize_ctx_t *ctx, void *flag, uint32_t
  * root and each device's rows of B up, runs the sharded GEMM, copies every device's column block into the dense
  * C and waits.  Device staging is cached in the handle and grows on demand.
  *
- * maize_mgpu_set: "chunk_rows" (multiple of 256, default 1024), "a_on_stream" (default 1); any other key is
+ * maize_mgpu_set: "chunk_rows" (multiple of 256, default 2048), "a_on_stream" (default 1); any other key is
  * passed to every device's context (maize_ctx_set).
  */
 typedef struct maize_mgpu maize_mgpu_t;

@@ -109,7 +109,7 @@ struct maize_ctx {
     uint32_t serpentine = 1;      // odd groups of row-blocks sweep the column-blocks backwards
     uint32_t tma_promotion = 3;   // CUtensorMapL2promotion of the operand maps: 0 none, 1 64 B, 2 128 B, 3 256 B
     uint32_t tail_split = 1;      // split the last partial round of pair tiles along K when pairs would idle
-    uint32_t chain_streams = 1;   // 2: maize_chain_forward alternates chunks between the caller's stream and a helper
+    uint32_t chain_streams = 2;   // 2: maize_chain_forward alternates chunks between the caller's stream and a helper
     cudaStream_t chain_helper = nullptr;
     cudaEvent_t chain_ev[3] = {};  // [0], [1]: "chunk published" per stream; [2]: fork / join
     uint64_t launches = 0;

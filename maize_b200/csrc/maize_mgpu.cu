@@ -77,7 +77,7 @@ struct maize_mgpu {
     StepArgs args;
     uint32_t chunks_total = 0;
     uint64_t steps = 0;
-    uint32_t chunk_rows = 1024;
+    uint32_t chunk_rows = 2048;
     bool a_on_stream = true;
     std::string err;
 };

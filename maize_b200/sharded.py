@@ -123,7 +123,7 @@ class NShardedGemm:
 
     def __init__(self, m: int, n: int, k: int, group=None, root: int = 0, slabs: int = 0,
                  gemm_fn: Optional[Callable] = None, device=None, ctx=None, transport: str = "auto",
-                 push_ctas: int = 0, mc_stages: int = 1, chain_rows: int = 1024,
+                 push_ctas: int = 0, mc_stages: int = 1, chain_rows: int = 2048,
                  chain_fused: bool = True, chain_streams: int = 2, **plan_args):
         import torch
         import torch.distributed as dist
