@@ -171,7 +171,9 @@ MAIZE_API maize_status_t maize_ctx_poll(maize_ctx_t *ctx, void *cuda_stream);
  * (default 1: the CTA-pair kernels write C through shared memory and TMA stores when C's rows are 16-byte
  * aligned), "tma_promotion" (L2 promotion of the operand tensor maps: 0 none, 1 64 B, 2 128 B, 3 256 B
  * = default), "chain_streams"
- * (1 or 2 = default: streams that maize_chain_forward alternates its chunks between), "repack_bytes" (size of an
+ * (1 or 2 = default: streams that maize_chain_forward alternates its chunks between), "chain_stagger"
+ * (default 1: when the source is all there, as on the root, the second stream starts half a chunk after the first,
+ * so that the two never publish at the same time and the link never idles), "repack_bytes" (size of an
  * optional scratch, allocated by this call, into which operands whose row pitch is not a multiple of 128
  * bytes are copied with an aligned pitch ahead of a large GEMM; 0 frees it), "debug_flags"
  * (performance diagnostics that make results WRONG: 1 = all loads hit one tile, 2 = no loads; refused

@@ -109,9 +109,10 @@ struct maize_ctx {
     uint32_t serpentine = 1;      // odd groups of row-blocks sweep the column-blocks backwards
     uint32_t tma_promotion = 3;   // CUtensorMapL2promotion of the operand maps: 0 none, 1 64 B, 2 128 B, 3 256 B
     uint32_t tail_split = 1;      // split the last partial round of pair tiles along K when pairs would idle
+    uint32_t chain_stagger = 1;   // two lanes on a source that is all there: offset them by half a chunk
     uint32_t chain_streams = 2;   // 2: maize_chain_forward alternates chunks between the caller's stream and a helper
     cudaStream_t chain_helper = nullptr;
-    cudaEvent_t chain_ev[3] = {};  // [0], [1]: "chunk published" per stream; [2]: fork / join
+    cudaEvent_t chain_ev[4] = {};  // [0], [1]: "chunk published" per stream; [2]: fork / join; [3]: half of the first chunk sent
     uint64_t launches = 0;
     EncodeTiledFn encode = nullptr;
     void *staging = nullptr;  // device staging for the *_host entry point
@@ -753,7 +754,7 @@ maize_status_t maize_ctx_create(int device, maize_ctx_t **out)
     ctx->repack_bytes = kDefaultRepackBytes;
     // MAIZE_<KEY>=<integer> in the environment presets a tunable of every context (same keys as maize_ctx_set)
     static const char *const kEnvKeys[] = {"pdl", "tma_store", "serpentine", "tail_split", "group_rows", "tma_promotion",
-                                           "chain_streams", "b_static", "timeout_ns", "max_ctas"};
+                                           "chain_streams", "chain_stagger", "b_static", "timeout_ns", "max_ctas"};
     for (const char *key : kEnvKeys) {
         std::string name = "MAIZE_";
         for (const char *c = key; *c; ++c)
@@ -1085,6 +1086,8 @@ maize_status_t maize_ctx_set(maize_ctx_t *ctx, const char *key, int64_t value)
         ctx->serpentine = value ? 1u : 0u;
     } else if (!strcmp(key, "tail_split")) {
         ctx->tail_split = value ? 1u : 0u;
+    } else if (!strcmp(key, "chain_stagger")) {
+        ctx->chain_stagger = value ? 1u : 0u;
     } else if (!strcmp(key, "chain_streams")) {
         if (value != 1 && value != 2)
             return fail(ctx, MAIZE_ERR_INVALID_ARG, "chain_streams: 1 or 2");
@@ -1136,6 +1139,8 @@ maize_status_t maize_ctx_get(const maize_ctx_t *ctx, const char *key, int64_t *v
         *value = ctx->d_profile ? 1 : 0;
     else if (!strcmp(key, "chain_streams"))
         *value = ctx->chain_streams;
+    else if (!strcmp(key, "chain_stagger"))
+        *value = ctx->chain_stagger;
     else if (!strcmp(key, "tail_split"))
         *value = ctx->tail_split;
     else if (!strcmp(key, "serpentine"))
@@ -1283,7 +1288,7 @@ maize_status_t maize_chain_forward(maize_ctx_t *ctx, const void *wait_flag, uint
         // order: the publishing kernel of chunk i waits (stream event) for the one of chunk i - 1.
         if (!ctx->chain_helper) {
             bool ok = cudaStreamCreateWithFlags(&ctx->chain_helper, cudaStreamNonBlocking) == cudaSuccess;
-            for (int i = 0; ok && i < 3; ++i)
+            for (int i = 0; ok && i < 4; ++i)
                 ok = cudaEventCreateWithFlags(&ctx->chain_ev[i], cudaEventDisableTiming) == cudaSuccess;
             if (!ok)
                 return fail_cuda(ctx, "creating the chain's helper stream / events", cudaGetLastError());
@@ -1304,8 +1309,19 @@ maize_status_t maize_chain_forward(maize_ctx_t *ctx, const void *wait_flag, uint
                                                           ctx->d_status, ctx->timeout_ns);
                 ctx->launches += 1;
             }
-            if ((e = cudaMemcpyAsync(static_cast<char *>(dst) + off, static_cast<const char *>(src) + off, nbytes,
-                                     cudaMemcpyDeviceToDevice, s)) != cudaSuccess)
+            if (!wait_flag && i == 0 && nbytes >= 32 && ctx->chain_stagger) {
+                // A source that is all there (the root's) would keep the two lanes in lock step: equal copies started
+                // together share the link and end together, and the link then idles while both lanes publish.  Offset
+                // the lanes by half a chunk: the second lane starts when the first half of chunk 0 has gone out.
+                const uint64_t half = (nbytes / 2) & ~uint64_t(15);
+                if ((e = cudaMemcpyAsync(dst, src, half, cudaMemcpyDeviceToDevice, s)) != cudaSuccess ||
+                    (e = cudaEventRecord(ctx->chain_ev[3], s)) != cudaSuccess ||
+                    (e = cudaStreamWaitEvent(lanes[1], ctx->chain_ev[3], 0)) != cudaSuccess ||
+                    (e = cudaMemcpyAsync(static_cast<char *>(dst) + half, static_cast<const char *>(src) + half,
+                                         nbytes - half, cudaMemcpyDeviceToDevice, s)) != cudaSuccess)
+                    return fail_cuda(ctx, "cudaMemcpyAsync (staggered first chunk)", e);
+            } else if ((e = cudaMemcpyAsync(static_cast<char *>(dst) + off, static_cast<const char *>(src) + off, nbytes,
+                                            cudaMemcpyDeviceToDevice, s)) != cudaSuccess)
                 return fail_cuda(ctx, "cudaMemcpyAsync", e);
             if (i > 0 && (e = cudaStreamWaitEvent(s, ctx->chain_ev[(i - 1) & 1u], 0)) != cudaSuccess)
                 return fail_cuda(ctx, "ordering the chain's publications", e);
