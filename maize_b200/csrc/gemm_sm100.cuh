@@ -14,7 +14,8 @@
 //     (cp_async.rs:98-253)
 //   ldmatrix + 2x mma.m16n8k16 per k-step           4x tcgen05.mma (128 x BN x 16) per 64-wide k-block,
 //     (gemm/mod.rs:18-33, mma/sm80.rs:136-160)        issued by one thread, fp32 accumulator in TMEM
-//   accumulators summed and dropped (main.rs:71)    tcgen05.ld -> cvt.rn.bf16x2 -> stores with row/col masks
+//   accumulators summed and dropped (main.rs:71)    tcgen05.ld -> cvt.rn.bf16x2 -> swizzled shared memory -> TMA stores
+//                                                     (aligned C rows) or masked direct stores (any other C)
 //
 // Roles (192 threads): warp 0 = TMA producer, warp 1 = MMA issuer and TMEM owner,
 // warps 2-5 = epilogue (warp w reads TMEM lanes 32*(w%4)...).  Two accumulator
@@ -38,7 +39,7 @@ struct GemmSmemLayout {
     // after the ring: epilogue staging, then full[STAGES], empty[STAGES], acc_full[2], acc_empty[2],
     // the TMEM base slot and the abort flag
     static constexpr uint32_t kStagingOffset = kRingBytes;
-    static constexpr uint32_t kBarOffset = kStagingOffset + kStageBytesTotal;
+    static constexpr uint32_t kBarOffset = kStagingOffset + kTmaStageBytesTotal;
     static constexpr uint32_t kNumBars = 2 * STAGES + 4;
     static constexpr uint32_t kTmemSlotOffset = kBarOffset + kNumBars * 8;
     static constexpr uint32_t kAbortOffset = kTmemSlotOffset + 4;
@@ -56,7 +57,7 @@ struct GemmSmemLayout {
 template <uint32_t BN, uint32_t STAGES, bool B_KN = false>
 __global__ void __launch_bounds__(kNumThreads, 1)
 gemm_bf16_sm100_1cta(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
-                     const GemmParams p)
+                     const __grid_constant__ CUtensorMap tma_c, const GemmParams p)
 {
     using L = GemmSmemLayout<BN, STAGES>;
     static_assert(BN % 32 == 0 && BN >= 32 && BN <= 256, "UMMA N for M = 128 must be a multiple of 16 up to 256");
@@ -90,6 +91,8 @@ gemm_bf16_sm100_1cta(const __grid_constant__ CUtensorMap tma_a, const __grid_con
     if (threadIdx.x == 0) {
         ptx::prefetch_tensormap(&tma_a);
         ptx::prefetch_tensormap(&tma_b);
+        if (p.c_tma_ok)
+            ptx::prefetch_tensormap(&tma_c);
         for (uint32_t s = 0; s < STAGES; ++s) {
             ptx::mbar_init(full_bar(s), 1);
             ptx::mbar_init(empty_bar(s), 1);
@@ -222,7 +225,9 @@ gemm_bf16_sm100_1cta(const __grid_constant__ CUtensorMap tma_a, const __grid_con
     } else {
         // ----------------------------------------------------------- epilogue --
         const uint32_t quarter = warp & 3u;  // TMEM lanes this warp may read
-        uint8_t *stage_warp = smem_gen + L::kStagingOffset + (warp - 2u) * kStageWarpBytes;
+        uint8_t *stage_warp = smem_gen + L::kStagingOffset + (warp - 2u) * kTmaStageWarpBytes;
+        const uint32_t stage_u32 = smem_base + L::kStagingOffset + (warp - 2u) * kTmaStageWarpBytes;
+        uint32_t store_buf = 0;
         uint32_t acc = 0, acc_phase = 0;
         bool ok = true;
         unsigned long long w_accfull = 0, w_drain = 0, n_tiles_done = 0;
@@ -239,8 +244,17 @@ gemm_bf16_sm100_1cta(const __grid_constant__ CUtensorMap tma_a, const __grid_con
                 break;
             ptx::tcgen05_fence_after();
             WaitTimer dt(prof);
-            drain_accumulator<BN>(p, stage_warp, tmem_base + acc * BN, quarter, lane, tc.m_blk * kBlockM,
-                                  tc.n_blk * BN);
+            if constexpr (BN % 64 == 0) {
+                if (p.c_tma_ok)
+                    drain_accumulator_tma<BN>(p, &tma_c, stage_u32, tmem_base + acc * BN, quarter, lane, tc.m_blk * kBlockM,
+                                              tc.n_blk * BN, store_buf);
+                else
+                    drain_accumulator<BN>(p, stage_warp, tmem_base + acc * BN, quarter, lane, tc.m_blk * kBlockM,
+                                          tc.n_blk * BN);
+            } else {
+                drain_accumulator<BN>(p, stage_warp, tmem_base + acc * BN, quarter, lane, tc.m_blk * kBlockM,
+                                      tc.n_blk * BN);
+            }
             dt.stop(w_drain);
             ++n_tiles_done;
             ptx::tcgen05_fence_before();
@@ -250,6 +264,8 @@ gemm_bf16_sm100_1cta(const __grid_constant__ CUtensorMap tma_a, const __grid_con
                 acc_phase ^= 1u;
             }
         }
+        if (p.c_tma_ok)
+            tma_store_drain(lane);  // the staging buffers must outlive the stores that read them
         if (prof && warp == 2 && lane == 0) {
             prof_out[kProfEpilogueWaitAccFull] = w_accfull;
             prof_out[kProfEpilogueDrain] = w_drain;

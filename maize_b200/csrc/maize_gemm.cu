@@ -105,7 +105,7 @@ struct maize_ctx {
     uint32_t pdl = 1;       // launch the GEMM kernels with programmatic stream serialization
     uint32_t b_static = 0;  // the caller guarantees that nothing earlier in the stream writes B (weights)
     uint32_t push_threads = 512;  // threads per CTA of the copy kernels of the multi-GPU path
-    uint32_t tma_store = 1;       // pair kernels: C through shared memory and TMA stores when its rows are 16-byte aligned
+    uint32_t tma_store = 1;       // tiled kernels: C through shared memory and TMA stores when its rows are 16-byte aligned
     uint32_t serpentine = 1;      // odd groups of row-blocks sweep the column-blocks backwards
     uint32_t tma_promotion = 3;   // CUtensorMapL2promotion of the operand maps: 0 none, 1 64 B, 2 128 B, 3 256 B
     uint32_t tail_split = 1;      // split the last partial round of pair tiles along K when pairs would idle
@@ -234,10 +234,10 @@ maize_status_t launch_kernel(maize_ctx_t *ctx, int variant_index, Kernel kernel,
 
 template <uint32_t BN, uint32_t STAGES, bool B_KN = false>
 maize_status_t launch_variant(maize_ctx_t *ctx, int variant_index, const CUtensorMap &ta, const CUtensorMap &tb,
-                              const GemmParams &p, uint32_t grid, cudaStream_t stream)
+                              const CUtensorMap &tc, const GemmParams &p, uint32_t grid, cudaStream_t stream)
 {
     return launch_kernel(ctx, variant_index, maize::gemm_bf16_sm100_1cta<BN, STAGES, B_KN>,
-                         maize::GemmSmemLayout<BN, STAGES>::kDynamicBytes, grid, stream, B_KN, p.pdl != 0, ta, tb, p);
+                         maize::GemmSmemLayout<BN, STAGES>::kDynamicBytes, grid, stream, B_KN, p.pdl != 0, ta, tb, tc, p);
 }
 
 // Tile width for the pair-split skinny kernel: the narrowest multiple of 32 for which one pair per tile
@@ -558,11 +558,12 @@ maize_status_t gemm_impl(maize_ctx_t *ctx, const void *a, uint64_t lda, const vo
     if (st != MAIZE_OK)
         return st;
 
-    // C leaves the pair kernels through shared memory and TMA stores when its rows are 16-byte aligned
+    // C leaves the tiled kernels (tiles of 64 columns and more) through shared memory and TMA stores when its
+    // rows are 16-byte aligned
     CUtensorMap tc;
     memset(&tc, 0, sizeof tc);
     const bool c_rows_aligned = ldc % 8 == 0 && reinterpret_cast<uintptr_t>(c) % 16 == 0;
-    const bool c_tma = ctx->tma_store && c_rows_aligned && kv.ctas_per_tile == 2 && ldc * 2 < (1ull << 40) &&
+    const bool c_tma = ctx->tma_store && c_rows_aligned && kv.block_n >= 64 && ldc * 2 < (1ull << 40) &&
                        make_store_map(ctx, &tc, c, m, n, ldc);
 
     GemmParams p;
@@ -657,9 +658,9 @@ maize_status_t gemm_impl(maize_ctx_t *ctx, const void *a, uint64_t lda, const vo
     }
     if (b_kn) {
         switch (vi) {
-        case 0: return launch_variant<256, 4, true>(ctx, vi, ta, tb, p, grid, stream);
-        case 1: return launch_variant<128, 6, true>(ctx, vi, ta, tb, p, grid, stream);
-        case 2: return launch_variant<64, 8, true>(ctx, vi, ta, tb, p, grid, stream);
+        case 0: return launch_variant<256, 4, true>(ctx, vi, ta, tb, tc, p, grid, stream);
+        case 1: return launch_variant<128, 6, true>(ctx, vi, ta, tb, tc, p, grid, stream);
+        case 2: return launch_variant<64, 8, true>(ctx, vi, ta, tb, tc, p, grid, stream);
         case 4:
             return launch_kernel(ctx, vi, maize::gemm_bf16_sm100_2cta<256, 1, 6, true>,
                                  maize::PairSmemLayout<256, 1, 6>::kDynamicBytes, grid, stream, true, p.pdl != 0, ta, tb, tc, p);
@@ -669,10 +670,10 @@ maize_status_t gemm_impl(maize_ctx_t *ctx, const void *a, uint64_t lda, const vo
         }
     }
     switch (vi) {
-    case 0: return launch_variant<256, 4>(ctx, vi, ta, tb, p, grid, stream);
-    case 1: return launch_variant<128, 6>(ctx, vi, ta, tb, p, grid, stream);
-    case 2: return launch_variant<64, 8>(ctx, vi, ta, tb, p, grid, stream);
-    case 3: return launch_variant<32, 8>(ctx, vi, ta, tb, p, grid, stream);
+    case 0: return launch_variant<256, 4>(ctx, vi, ta, tb, tc, p, grid, stream);
+    case 1: return launch_variant<128, 6>(ctx, vi, ta, tb, tc, p, grid, stream);
+    case 2: return launch_variant<64, 8>(ctx, vi, ta, tb, tc, p, grid, stream);
+    case 3: return launch_variant<32, 8>(ctx, vi, ta, tb, tc, p, grid, stream);
     case 4:
         return launch_kernel(ctx, vi, maize::gemm_bf16_sm100_2cta<256, 1, 6>,
                              maize::PairSmemLayout<256, 1, 6>::kDynamicBytes, grid, stream, false, p.pdl != 0, ta, tb, tc, p);

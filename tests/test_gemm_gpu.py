@@ -335,10 +335,10 @@ def test_canaries_around_c(ctx, oracle):
                   oracle.max_abs_bf16(b), "strided C")
 
 
-@pytest.mark.parametrize("force", [5, 6, 10])
+@pytest.mark.parametrize("force", [1, 2, 3, 5, 6, 10])
 @pytest.mark.parametrize("tma_store", [1, 0])
 def test_canaries_around_c_with_aligned_rows(ctx, oracle, force, tma_store):
-    """C rows 16-byte aligned (ldc % 8 == 0) but narrower than the pitch and with ragged M and N: the pair kernels
+    """C rows 16-byte aligned (ldc % 8 == 0) but narrower than the pitch and with ragged M and N: the tiled kernels
     write such a C through shared memory and TMA stores, which must clip at M and N exactly; the direct-store
     path ("tma_store" = 0) is held to the same."""
     import torch
