@@ -18,6 +18,7 @@
 #include "gemm_sm100.cuh"
 #include "gemm_sm100_2cta.cuh"
 #include "gemm_sm100_2cta_tail.cuh"
+#include "gemm_sm100_2cta_wide.cuh"
 #include "gemm_sm100_skinny.cuh"
 #include "gemm_sm100_skinny_pair.cuh"
 #include "gemm_sm100_skinny_pair_tall.cuh"
@@ -57,6 +58,8 @@ const KernelVariant kVariants[] = {
     {"sm100_2cta_256x256x128_s3_tail", 256, 256, 128, 2},
     // the pair-split decode kernel for 32 < M <= 128: A tile loaded once, halves exchanged through the whole ring
     {"sm100_skinny_pair_m128_128xNx64_s4", 128, 256, 256, 2},
+    // 256 x 512 per CTA pair, one accumulator filling tensor memory: a quarter less L2 traffic per flop, for long K
+    {"sm100_2cta_256x512x64_s4", 256, 512, 128, 2},
 };
 constexpr int kPairWide = 5;     // index of the CTA-pair kernel with 128-wide stages
 constexpr int kFirstSkinny = 6;  // indices of the skinny variants
@@ -64,6 +67,7 @@ constexpr int kLastSkinny = 7;
 constexpr int kSkinnyPair = 8;
 constexpr int kPairTail = 9;
 constexpr int kSkinnyPairTall = 10;
+constexpr int kPairWideTile = 11;
 constexpr int kNumVariants = static_cast<int>(sizeof(kVariants) / sizeof(kVariants[0]));
 constexpr int kMaxProfileCtas = 1024;
 constexpr int kMaxHostSlabs = 16;  // row slabs of A / C that the host entry point pipelines over PCIe
@@ -105,6 +109,7 @@ struct maize_ctx {
     uint32_t pdl = 1;       // launch the GEMM kernels with programmatic stream serialization
     uint32_t b_static = 0;  // the caller guarantees that nothing earlier in the stream writes B (weights)
     uint32_t push_threads = 512;  // threads per CTA of the copy kernels of the multi-GPU path
+    uint32_t wide_tile = 0;       // use the 256 x 512 pair tile where it suits (long K, full rounds)
     uint32_t tma_store = 1;       // tiled kernels: C through shared memory and TMA stores when its rows are 16-byte aligned
     uint32_t serpentine = 1;      // odd groups of row-blocks sweep the column-blocks backwards
     uint32_t tma_promotion = 3;   // CUtensorMapL2promotion of the operand maps: 0 none, 1 64 B, 2 128 B, 3 256 B
@@ -263,6 +268,22 @@ uint32_t skinny_pair_tile(uint32_t sms, uint32_t n, uint32_t k, double *est_pair
     return bn;
 }
 
+// Whether the 256 x 512 pair tile suits a shape: K long enough that the exposed part of its epilogue is small,
+// little of the last column block wasted, and whole rounds of tiles nearly full (it has no K split for a partial
+// last round).
+bool wide_tile_suits(uint32_t sms, uint32_t m, uint32_t n, uint32_t k)
+{
+    const uint64_t pairs = sms / 2 ? sms / 2 : 1;
+    if (k < 2048 || m <= 128 || n < 512)
+        return false;
+    const uint64_t cols = (uint64_t(n) + 511) / 512 * 512;
+    if (double(n) < 0.94 * double(cols))
+        return false;
+    const uint64_t tiles = ((uint64_t(m) + 255) / 256) * (cols / 512);
+    const uint64_t rounds = (tiles + pairs - 1) / pairs;
+    return double(tiles) >= 0.92 * double(rounds * pairs);
+}
+
 int pick_variant(const maize_ctx_t *ctx, uint32_t m, uint32_t n, uint32_t k)
 {
     if (ctx && ctx->force_kernel >= 1 && ctx->force_kernel <= kNumVariants)
@@ -297,7 +318,9 @@ int pick_variant(const maize_ctx_t *ctx, uint32_t m, uint32_t n, uint32_t k)
     const uint64_t pairs = sms / 2 ? sms / 2 : 1;
     const uint64_t waves_pair = (((uint64_t(m) + 255) / 256) * tiles_n + pairs - 1) / pairs;
     const uint64_t waves_single = (tiles_m * tiles_n + sms - 1) / sms;
-    return waves_pair <= waves_single ? kPairWide : 0;
+    if (waves_pair > waves_single)
+        return 0;
+    return (ctx && ctx->wide_tile && wide_tile_suits(sms, m, n, k)) ? kPairWideTile : kPairWide;
 }
 
 template <bool REPL, uint32_t STAGES>
@@ -384,7 +407,7 @@ maize_status_t gemm_impl(maize_ctx_t *ctx, const void *a, uint64_t lda, const vo
     int vi = pick_variant(ctx, m, n, k);
     if (gate) {
         // only the tiled kernels watch the gate; a forced or chosen decode kernel is replaced
-        if (vi >= kFirstSkinny && vi != kPairTail)
+        if (vi >= kFirstSkinny && vi != kPairTail && vi != kPairWideTile)
             vi = n > 128 ? 0 : (n > 64 ? 1 : (n > 32 ? 2 : 3));
     }
     if (b_kn) {
@@ -392,11 +415,16 @@ maize_status_t gemm_impl(maize_ctx_t *ctx, const void *a, uint64_t lda, const vo
         if (ctx->force_kernel != 0) {
             if (vi == 3 || vi >= kFirstSkinny)
                 return fail(ctx, MAIZE_ERR_UNSUPPORTED, "this kernel variant does not take a K x N matrix B");
-        } else if (vi >= kFirstSkinny && vi != kPairTail) {
+        } else if (vi >= kFirstSkinny && vi != kPairTail && vi != kPairWideTile) {
             vi = n > 128 ? 0 : (n > 64 ? 1 : 2);
         } else if (vi == 3) {
             vi = 2;
         }
+    }
+    if (vi == kPairWideTile && b_kn) {
+        if (ctx->force_kernel != 0)
+            return fail(ctx, MAIZE_ERR_UNSUPPORTED, "the 256 x 512 pair kernel does not take a K x N matrix B");
+        vi = kPairWide;
     }
     const KernelVariant &kv = kVariants[vi];
 
@@ -656,6 +684,9 @@ maize_status_t gemm_impl(maize_ctx_t *ctx, const void *a, uint64_t lda, const vo
             return MAIZE_OK;
         }
     }
+    if (vi == kPairWideTile)
+        return launch_kernel(ctx, vi, maize::gemm_bf16_sm100_2cta_wide<4>, maize::WideSmemLayout<4>::kDynamicBytes, grid,
+                             stream, false, p.pdl != 0, ta, tb, tc, p);
     if (b_kn) {
         switch (vi) {
         case 0: return launch_variant<256, 4, true>(ctx, vi, ta, tb, tc, p, grid, stream);
@@ -754,7 +785,7 @@ maize_status_t maize_ctx_create(int device, maize_ctx_t **out)
     }
     ctx->repack_bytes = kDefaultRepackBytes;
     // MAIZE_<KEY>=<integer> in the environment presets a tunable of every context (same keys as maize_ctx_set)
-    static const char *const kEnvKeys[] = {"pdl", "tma_store", "serpentine", "tail_split", "group_rows", "tma_promotion",
+    static const char *const kEnvKeys[] = {"pdl", "tma_store", "wide_tile", "serpentine", "tail_split", "group_rows", "tma_promotion",
                                            "chain_streams", "chain_stagger", "b_static", "timeout_ns", "max_ctas"};
     for (const char *key : kEnvKeys) {
         std::string name = "MAIZE_";
@@ -1081,6 +1112,8 @@ maize_status_t maize_ctx_set(maize_ctx_t *ctx, const char *key, int64_t value)
         if (value < 0 || value > 3)
             return fail(ctx, MAIZE_ERR_INVALID_ARG, "tma_promotion: 0 (none), 1 (64 B), 2 (128 B) or 3 (256 B)");
         ctx->tma_promotion = static_cast<uint32_t>(value);
+    } else if (!strcmp(key, "wide_tile")) {
+        ctx->wide_tile = value ? 1u : 0u;
     } else if (!strcmp(key, "tma_store")) {
         ctx->tma_store = value ? 1u : 0u;
     } else if (!strcmp(key, "serpentine")) {
@@ -1148,6 +1181,8 @@ maize_status_t maize_ctx_get(const maize_ctx_t *ctx, const char *key, int64_t *v
         *value = ctx->serpentine;
     else if (!strcmp(key, "tma_store"))
         *value = ctx->tma_store;
+    else if (!strcmp(key, "wide_tile"))
+        *value = ctx->wide_tile;
     else if (!strcmp(key, "tma_promotion"))
         *value = ctx->tma_promotion;
     else if (!strcmp(key, "repack_bytes"))
