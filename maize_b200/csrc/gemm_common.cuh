@@ -83,6 +83,7 @@ struct GemmParams {
     uint32_t pdl = 0;         // 1: launched with programmatic stream serialization (see the kernels' set-up)
     uint32_t serpentine = 0;  // 1: odd groups of row-blocks sweep the column-blocks backwards
     uint32_t c_vec_ok;  // 1: every C row starts 16-byte aligned (ldc % 8 == 0 and base aligned)
+    uint32_t c_evict_first = 0;  // 1: TMA stores of C carry an evict-first L2 hint
     uint32_t c_tma_ok = 0;  // 1: the kernel's C tensor map is valid: full tiles leave through shared memory and TMA stores
     DeviceStatus *status;
     uint64_t timeout_ns;
@@ -327,7 +328,12 @@ __device__ __forceinline__ void drain_accumulator_tma(const GemmParams &p, const
         ptx::fence_proxy_async_shared();
         __syncwarp();
         if (lane == 0) {
-            ptx::tma_store_2d(tma_c, base, static_cast<int32_t>(col0), static_cast<int32_t>(row0));
+            // C passes through L2 once: its lines are the first to go, so that they do not push operand panels out
+            if (p.c_evict_first)
+                ptx::tma_store_2d_hint(tma_c, base, static_cast<int32_t>(col0), static_cast<int32_t>(row0),
+                                       ptx::policy_evict_first());
+            else
+                ptx::tma_store_2d(tma_c, base, static_cast<int32_t>(col0), static_cast<int32_t>(row0));
             ptx::bulk_commit_group();
         }
         buf ^= 1u;

@@ -154,6 +154,16 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, uint32_t sm
                  : "memory");
 }
 
+// Same with an L2 eviction-priority hint (createpolicy value) for the lines written.
+__device__ __forceinline__ void tma_store_2d_hint(const CUtensorMap *map, uint32_t smem_src, int32_t x, int32_t y,
+                                                  uint64_t policy)
+{
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group.L2::cache_hint [%0, {%2, %3}], [%1], %4;" ::"l"(
+                     reinterpret_cast<uint64_t>(map)),
+                 "r"(smem_src), "r"(x), "r"(y), "l"(policy)
+                 : "memory");
+}
+
 __device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 
 // Until at most N of this thread's bulk groups are still READING their shared-memory source.
