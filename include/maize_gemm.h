@@ -171,7 +171,8 @@ MAIZE_API maize_status_t maize_ctx_poll(maize_ctx_t *ctx, void *cuda_stream);
  * (default 1: the CTA-pair kernels write C through shared memory and TMA stores when C's rows are 16-byte
  * aligned), "c_evict_first" (default 1: those stores carry an evict-first L2 hint, C passes through L2 once),
  * "wide_tile" (default 1: GEMMs of up to about a millisecond with long K and nearly full rounds of tiles use a
- * 256 x 512 tile per CTA pair, which moves a quarter less data from L2 per flop), "tma_promotion" (L2 promotion of the operand tensor maps: 0 none, 1 64 B, 2 128 B, 3 256 B
+ * 256 x 512 tile per CTA pair, which moves a quarter less data from L2 per flop; "wide_max_gflop", default 2200,
+ * is the largest 2MNK / 1e9 that takes it), "tma_promotion" (L2 promotion of the operand tensor maps: 0 none, 1 64 B, 2 128 B, 3 256 B
  * = default), "chain_streams"
  * (1 or 2 = default: streams that maize_chain_forward alternates its chunks between), "chain_stagger"
  * (default 1: when the source is all there, as on the root, the second stream starts half a chunk after the first,

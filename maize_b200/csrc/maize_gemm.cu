@@ -110,6 +110,7 @@ struct maize_ctx {
     uint32_t b_static = 0;  // the caller guarantees that nothing earlier in the stream writes B (weights)
     uint32_t push_threads = 512;  // threads per CTA of the copy kernels of the multi-GPU path
     uint32_t c_evict_first = 1;   // TMA stores of C carry an evict-first L2 hint
+    uint64_t wide_max_gflop = 2200;  // largest GEMM (2MNK / 1e9) that takes the wide tile
     uint32_t wide_tile = 1;       // use the 256 x 512 pair tile where it suits (long K, full rounds, about a millisecond of work)
     uint32_t tma_store = 1;       // tiled kernels: C through shared memory and TMA stores when its rows are 16-byte aligned
     uint32_t serpentine = 1;      // odd groups of row-blocks sweep the column-blocks backwards
@@ -272,7 +273,7 @@ uint32_t skinny_pair_tile(uint32_t sms, uint32_t n, uint32_t k, double *est_pair
 // Whether the 256 x 512 pair tile suits a shape: K long enough that the exposed part of its epilogue is small,
 // little of the last column block wasted, and whole rounds of tiles nearly full (it has no K split for a partial
 // last round).
-bool wide_tile_suits(uint32_t sms, uint32_t m, uint32_t n, uint32_t k)
+bool wide_tile_suits(uint32_t sms, uint32_t m, uint32_t n, uint32_t k, uint64_t max_gflop)
 {
     const uint64_t pairs = sms / 2 ? sms / 2 : 1;
     if (k < 2048 || m <= 128 || n < 512)
@@ -280,7 +281,7 @@ bool wide_tile_suits(uint32_t sms, uint32_t m, uint32_t n, uint32_t k)
     // Measured: on GEMMs of about a millisecond (8192^3) the wide tile gains 6 % (fewer bytes moved, higher clock
     // under the power cap); on multi-millisecond GEMMs run back to back the part settles at a clock that no longer
     // follows the bytes, and the 256 x 256 kernel's better hidden epilogue wins by 1-3 %.
-    if (2.0 * double(m) * double(n) * double(k) > 2.2e12)
+    if (2.0 * double(m) * double(n) * double(k) > double(max_gflop) * 1e9)
         return false;
     const uint64_t cols = (uint64_t(n) + 511) / 512 * 512;
     if (double(n) < 0.94 * double(cols))
@@ -326,7 +327,7 @@ int pick_variant(const maize_ctx_t *ctx, uint32_t m, uint32_t n, uint32_t k)
     const uint64_t waves_single = (tiles_m * tiles_n + sms - 1) / sms;
     if (waves_pair > waves_single)
         return 0;
-    return (ctx && ctx->wide_tile && wide_tile_suits(sms, m, n, k)) ? kPairWideTile : kPairWide;
+    return (ctx && ctx->wide_tile && wide_tile_suits(sms, m, n, k, ctx->wide_max_gflop)) ? kPairWideTile : kPairWide;
 }
 
 template <bool REPL, uint32_t STAGES>
@@ -792,7 +793,7 @@ maize_status_t maize_ctx_create(int device, maize_ctx_t **out)
     }
     ctx->repack_bytes = kDefaultRepackBytes;
     // MAIZE_<KEY>=<integer> in the environment presets a tunable of every context (same keys as maize_ctx_set)
-    static const char *const kEnvKeys[] = {"pdl", "tma_store", "wide_tile", "c_evict_first", "serpentine", "tail_split", "group_rows", "tma_promotion",
+    static const char *const kEnvKeys[] = {"pdl", "tma_store", "wide_tile", "wide_max_gflop", "c_evict_first", "serpentine", "tail_split", "group_rows", "tma_promotion",
                                            "chain_streams", "chain_stagger", "b_static", "timeout_ns", "max_ctas"};
     for (const char *key : kEnvKeys) {
         std::string name = "MAIZE_";
@@ -1121,6 +1122,10 @@ maize_status_t maize_ctx_set(maize_ctx_t *ctx, const char *key, int64_t value)
         ctx->tma_promotion = static_cast<uint32_t>(value);
     } else if (!strcmp(key, "c_evict_first")) {
         ctx->c_evict_first = value ? 1u : 0u;
+    } else if (!strcmp(key, "wide_max_gflop")) {
+        if (value < 0)
+            return fail(ctx, MAIZE_ERR_INVALID_ARG, "wide_max_gflop must be >= 0");
+        ctx->wide_max_gflop = static_cast<uint64_t>(value);
     } else if (!strcmp(key, "wide_tile")) {
         ctx->wide_tile = value ? 1u : 0u;
     } else if (!strcmp(key, "tma_store")) {
@@ -1192,6 +1197,8 @@ maize_status_t maize_ctx_get(const maize_ctx_t *ctx, const char *key, int64_t *v
         *value = ctx->tma_store;
     else if (!strcmp(key, "wide_tile"))
         *value = ctx->wide_tile;
+    else if (!strcmp(key, "wide_max_gflop"))
+        *value = static_cast<int64_t>(ctx->wide_max_gflop);
     else if (!strcmp(key, "c_evict_first"))
         *value = ctx->c_evict_first;
     else if (!strcmp(key, "tma_promotion"))
