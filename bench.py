@@ -71,7 +71,7 @@ def parse_args():
     p.add_argument("--mc-stages", type=int, default=1, choices=[1, 2],
                    help="multimem transport: 2 = root scatters chunks and every GPU multicasts its own, 1 = root multicasts all")
     p.add_argument("--chain-rows", type=int, default=2048, help="chain transport: rows of A per forwarded chunk")
-    p.add_argument("--chain-streams", type=int, default=2, choices=[1, 2],
+    p.add_argument("--chain-streams", type=int, default=2, choices=[1, 2, 3, 4],
                    help="chain transport: streams the forwarded chunks alternate between")
     p.add_argument("--chain-fused", type=int, default=1, choices=[0, 1],
                    help="chain transport: 1 = one gated GEMM launch per step (waits for rows inside the kernel), 0 = one per slab")

@@ -170,13 +170,14 @@ MAIZE_API maize_status_t maize_ctx_poll(maize_ctx_t *ctx, void *cuda_stream);
  * of 256 x 256 tiles would leave CTA pairs idle, its tiles are split along K over them), "tma_store"
  * (default 1: the CTA-pair kernels write C through shared memory and TMA stores when C's rows are 16-byte
  * aligned), "c_evict_first" (default 1: those stores carry an evict-first L2 hint, C passes through L2 once),
- * "wide_tile" (default 1: GEMMs of up to about a millisecond with long K and nearly full rounds of tiles use a
- * 256 x 512 tile per CTA pair, which moves a quarter less data from L2 per flop; "wide_max_gflop", default 2200,
- * is the largest 2MNK / 1e9 that takes it), "tma_promotion" (L2 promotion of the operand tensor maps: 0 none, 1 64 B, 2 128 B, 3 256 B
+ * "wide_tile" (default 1: GEMMs with long K and nearly full rounds of tiles use a 256 x 512 tile per CTA
+ * pair, which moves a quarter less data from L2 per flop; "wide_max_gflop", default 1000000, is the largest
+ * 2MNK / 1e9 that takes it: multi-millisecond GEMMs run back to back for seconds are 1-3 % faster on the 256 x 256
+ * tile), "tma_promotion" (L2 promotion of the operand tensor maps: 0 none, 1 64 B, 2 128 B, 3 256 B
  * = default), "chain_streams"
- * (1 or 2 = default: streams that maize_chain_forward alternates its chunks between), "chain_stagger"
- * (default 1: when the source is all there, as on the root, the second stream starts half a chunk after the first,
- * so that the two never publish at the same time and the link never idles), "repack_bytes" (size of an
+ * (1 to 4, default 2: streams that maize_chain_forward deals its chunks over), "chain_stagger"
+ * (default 1: when the source is all there, as on the root, the streams start a fraction of a chunk apart,
+ * so that they never publish at the same time and the link never idles), "repack_bytes" (size of an
  * optional scratch, allocated by this call, into which operands whose row pitch is not a multiple of 128
  * bytes are copied with an aligned pitch ahead of a large GEMM; 0 frees it), "debug_flags"
  * (performance diagnostics that make results WRONG: 1 = all loads hit one tile, 2 = no loads; refused
@@ -256,8 +257,8 @@ MAIZE_API maize_status_t maize_gemm_bf16_gated(maize_ctx_t *ctx, const void *a, 
  * (i = 0, 1, ...) wait (bounded, if `wait_flag` is not NULL) until the local word `wait_flag` has reached
  * first_value + i, copy the chunk to `dst` + its offset (copy engines; `dst` is the next rank's landing buffer
  * through its peer mapping), then store first_value + i in `dst_flag` (the next rank's "chunks landed" word).
- * Everything is enqueued in one call, on `cuda_stream` and, with "chain_streams" = 2, alternately on a helper
- * stream of the context that forks from and joins `cuda_stream` (counts are still published in chunk order). */
+ * Everything is enqueued in one call, on `cuda_stream` and, with "chain_streams" > 1, round robin on helper
+ * streams of the context that fork from and join `cuda_stream` (counts are still published in chunk order). */
 MAIZE_API maize_status_t maize_chain_forward(maize_ctx_t *ctx, const void *wait_flag, uint32_t first_value, void *dst,
                                              const void *src, uint64_t total_bytes, uint64_t chunk_bytes,
                                              void *dst_flag, void *cuda_stream);

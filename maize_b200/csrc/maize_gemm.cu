@@ -70,6 +70,7 @@ constexpr int kSkinnyPairTall = 10;
 constexpr int kPairWideTile = 11;
 constexpr int kNumVariants = static_cast<int>(sizeof(kVariants) / sizeof(kVariants[0]));
 constexpr int kMaxProfileCtas = 1024;
+constexpr uint32_t kMaxChainLanes = 4;  // streams maize_chain_forward may spread its chunks over
 constexpr int kMaxHostSlabs = 16;  // row slabs of A / C that the host entry point pipelines over PCIe
 constexpr size_t kPartialsBytes = size_t(32) << 20;  // stream-K scratch per context
 constexpr size_t kDefaultRepackBytes = size_t(128) << 20;  // scratch of the pitch-aligning pre-pass per context
@@ -110,7 +111,7 @@ struct maize_ctx {
     uint32_t b_static = 0;  // the caller guarantees that nothing earlier in the stream writes B (weights)
     uint32_t push_threads = 512;  // threads per CTA of the copy kernels of the multi-GPU path
     uint32_t c_evict_first = 1;   // TMA stores of C carry an evict-first L2 hint
-    uint64_t wide_max_gflop = 2200;  // largest GEMM (2MNK / 1e9) that takes the wide tile
+    uint64_t wide_max_gflop = 1000000;  // largest GEMM (2MNK / 1e9) that takes the wide tile
     uint32_t wide_tile = 1;       // use the 256 x 512 pair tile where it suits (long K, full rounds, about a millisecond of work)
     uint32_t tma_store = 1;       // tiled kernels: C through shared memory and TMA stores when its rows are 16-byte aligned
     uint32_t serpentine = 1;      // odd groups of row-blocks sweep the column-blocks backwards
@@ -118,8 +119,10 @@ struct maize_ctx {
     uint32_t tail_split = 1;      // split the last partial round of pair tiles along K when pairs would idle
     uint32_t chain_stagger = 1;   // two lanes on a source that is all there: offset them by half a chunk
     uint32_t chain_streams = 2;   // 2: maize_chain_forward alternates chunks between the caller's stream and a helper
-    cudaStream_t chain_helper = nullptr;
-    cudaEvent_t chain_ev[4] = {};  // [0], [1]: "chunk published" per stream; [2]: fork / join; [3]: half of the first chunk sent
+    cudaStream_t chain_helper[kMaxChainLanes] = {};  // lanes 1 .. L-1 of maize_chain_forward (lane 0 is the caller's stream)
+    cudaEvent_t chain_ev_fork = nullptr;             // the caller's stream as of the call
+    cudaEvent_t chain_ev_pub[kMaxChainLanes] = {};   // "chunk published" per lane
+    cudaEvent_t chain_ev_part[kMaxChainLanes] = {};  // pieces of the first chunk sent (offsets the lanes)
     uint64_t launches = 0;
     EncodeTiledFn encode = nullptr;
     void *staging = nullptr;  // device staging for the *_host entry point
@@ -278,9 +281,10 @@ bool wide_tile_suits(uint32_t sms, uint32_t m, uint32_t n, uint32_t k, uint64_t 
     const uint64_t pairs = sms / 2 ? sms / 2 : 1;
     if (k < 2048 || m <= 128 || n < 512)
         return false;
-    // Measured: on GEMMs of about a millisecond (8192^3) the wide tile gains 6 % (fewer bytes moved, higher clock
-    // under the power cap); on multi-millisecond GEMMs run back to back the part settles at a clock that no longer
-    // follows the bytes, and the 256 x 256 kernel's better hidden epilogue wins by 1-3 %.
+    // Measured: in fresh runs of tens to hundreds of milliseconds the wide tile gains 5-6 % on 8192^3 and 16384^3
+    // (fewer bytes moved, higher clock under the power cap).  Run back to back for seconds the part settles at a
+    // clock that no longer follows the bytes, and the 256 x 256 kernel's better hidden epilogue is then 1-3 % ahead
+    // on multi-millisecond GEMMs: "wide_max_gflop" lets a caller in that regime cap the size.
     if (2.0 * double(m) * double(n) * double(k) > double(max_gflop) * 1e9)
         return false;
     const uint64_t cols = (uint64_t(n) + 511) / 512 * 512;
@@ -826,11 +830,16 @@ void maize_ctx_destroy(maize_ctx_t *ctx)
         cudaFree(ctx->staging);
     if (ctx->repack)
         cudaFree(ctx->repack);
-    if (ctx->chain_helper)
-        cudaStreamDestroy(ctx->chain_helper);
-    for (cudaEvent_t ev : ctx->chain_ev)
-        if (ev)
-            cudaEventDestroy(ev);
+    for (uint32_t j = 0; j < kMaxChainLanes; ++j) {
+        if (ctx->chain_helper[j])
+            cudaStreamDestroy(ctx->chain_helper[j]);
+        if (ctx->chain_ev_pub[j])
+            cudaEventDestroy(ctx->chain_ev_pub[j]);
+        if (ctx->chain_ev_part[j])
+            cudaEventDestroy(ctx->chain_ev_part[j]);
+    }
+    if (ctx->chain_ev_fork)
+        cudaEventDestroy(ctx->chain_ev_fork);
     if (ctx->copy_in)
         cudaStreamDestroy(ctx->copy_in);
     if (ctx->copy_out)
@@ -1137,8 +1146,8 @@ maize_status_t maize_ctx_set(maize_ctx_t *ctx, const char *key, int64_t value)
     } else if (!strcmp(key, "chain_stagger")) {
         ctx->chain_stagger = value ? 1u : 0u;
     } else if (!strcmp(key, "chain_streams")) {
-        if (value != 1 && value != 2)
-            return fail(ctx, MAIZE_ERR_INVALID_ARG, "chain_streams: 1 or 2");
+        if (value < 1 || value > static_cast<int64_t>(kMaxChainLanes))
+            return fail(ctx, MAIZE_ERR_INVALID_ARG, "chain_streams: 1 to 4");
         ctx->chain_streams = static_cast<uint32_t>(value);
     } else if (!strcmp(key, "push_threads")) {
         if (value < 32 || value > 512 || value % 32 != 0)
@@ -1336,60 +1345,73 @@ maize_status_t maize_chain_forward(maize_ctx_t *ctx, const void *wait_flag, uint
         return fail(ctx, MAIZE_ERR_INVALID_ARG, "chain: bad pointer or chunk size");
     DeviceGuard guard(ctx->device);
     cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
-    if (ctx->chain_streams == 2 && total_bytes > chunk_bytes) {
-        // Chunks alternate between the caller's stream and a helper stream, so that the small kernels around one
-        // chunk's copy run while the other stream's copy keeps the link busy.  Counts are still published in chunk
-        // order: the publishing kernel of chunk i waits (stream event) for the one of chunk i - 1.
-        if (!ctx->chain_helper) {
-            bool ok = cudaStreamCreateWithFlags(&ctx->chain_helper, cudaStreamNonBlocking) == cudaSuccess;
-            for (int i = 0; ok && i < 4; ++i)
-                ok = cudaEventCreateWithFlags(&ctx->chain_ev[i], cudaEventDisableTiming) == cudaSuccess;
+    if (ctx->chain_streams >= 2 && total_bytes > chunk_bytes) {
+        // Chunks go round robin over L lanes (the caller's stream and L - 1 helper streams), so that the small
+        // kernels around one chunk's copy run while other lanes' copies keep the link busy, and several copies are
+        // in flight at once.  Counts are still published in chunk order: the publishing kernel of chunk i waits
+        // (stream event) for the one of chunk i - 1.
+        const uint32_t L = ctx->chain_streams;
+        if (!ctx->chain_ev_fork) {
+            bool ok = cudaEventCreateWithFlags(&ctx->chain_ev_fork, cudaEventDisableTiming) == cudaSuccess;
+            for (uint32_t j = 0; ok && j < kMaxChainLanes; ++j)
+                ok = cudaEventCreateWithFlags(&ctx->chain_ev_pub[j], cudaEventDisableTiming) == cudaSuccess &&
+                     cudaEventCreateWithFlags(&ctx->chain_ev_part[j], cudaEventDisableTiming) == cudaSuccess &&
+                     (j == 0 || cudaStreamCreateWithFlags(&ctx->chain_helper[j], cudaStreamNonBlocking) == cudaSuccess);
             if (!ok)
-                return fail_cuda(ctx, "creating the chain's helper stream / events", cudaGetLastError());
+                return fail_cuda(ctx, "creating the chain's helper streams / events", cudaGetLastError());
         }
-        cudaStream_t lanes[2] = {stream, ctx->chain_helper};
+        cudaStream_t lanes[kMaxChainLanes];
+        lanes[0] = stream;
+        for (uint32_t j = 1; j < L; ++j)
+            lanes[j] = ctx->chain_helper[j];
         cudaError_t e;
-        // fork: the helper starts after whatever the caller queued on its stream before this call
-        if ((e = cudaEventRecord(ctx->chain_ev[2], stream)) != cudaSuccess ||
-            (e = cudaStreamWaitEvent(ctx->chain_helper, ctx->chain_ev[2], 0)) != cudaSuccess)
-            return fail_cuda(ctx, "forking the chain's helper stream", e);
+        // fork: the helpers start after whatever the caller queued on its stream before this call
+        if ((e = cudaEventRecord(ctx->chain_ev_fork, stream)) != cudaSuccess)
+            return fail_cuda(ctx, "forking the chain's helper streams", e);
+        for (uint32_t j = 1; j < L; ++j)
+            if ((e = cudaStreamWaitEvent(lanes[j], ctx->chain_ev_fork, 0)) != cudaSuccess)
+                return fail_cuda(ctx, "forking the chain's helper streams", e);
         uint32_t v = first_value;
         uint32_t i = 0;
         for (uint64_t off = 0; off < total_bytes; off += chunk_bytes, ++v, ++i) {
             const uint64_t nbytes = total_bytes - off < chunk_bytes ? total_bytes - off : chunk_bytes;
-            cudaStream_t s = lanes[i & 1u];
+            const uint32_t lane = i % L;
+            cudaStream_t s = lanes[lane];
             if (wait_flag) {
                 maize::chain_step_kernel<<<1, 32, 0, s>>>(nullptr, 0, static_cast<const uint32_t *>(wait_flag), v,
                                                           ctx->d_status, ctx->timeout_ns);
                 ctx->launches += 1;
             }
-            if (!wait_flag && i == 0 && nbytes >= 32 && ctx->chain_stagger) {
-                // A source that is all there (the root's) would keep the two lanes in lock step: equal copies started
-                // together share the link and end together, and the link then idles while both lanes publish.  Offset
-                // the lanes by half a chunk: the second lane starts when the first half of chunk 0 has gone out.
-                const uint64_t half = (nbytes / 2) & ~uint64_t(15);
-                if ((e = cudaMemcpyAsync(dst, src, half, cudaMemcpyDeviceToDevice, s)) != cudaSuccess ||
-                    (e = cudaEventRecord(ctx->chain_ev[3], s)) != cudaSuccess ||
-                    (e = cudaStreamWaitEvent(lanes[1], ctx->chain_ev[3], 0)) != cudaSuccess ||
-                    (e = cudaMemcpyAsync(static_cast<char *>(dst) + half, static_cast<const char *>(src) + half,
-                                         nbytes - half, cudaMemcpyDeviceToDevice, s)) != cudaSuccess)
-                    return fail_cuda(ctx, "cudaMemcpyAsync (staggered first chunk)", e);
+            if (!wait_flag && i == 0 && nbytes >= 16 * L && ctx->chain_stagger) {
+                // A source that is all there (the root's) would keep the lanes in lock step: equal copies started
+                // together share the link and end together, and the link then idles while all lanes publish.  Offset
+                // them: chunk 0 goes out in L pieces, and lane j starts when piece j has gone out.
+                const uint64_t piece = (nbytes / L) & ~uint64_t(15);
+                for (uint32_t j = 0; j < L; ++j) {
+                    const uint64_t lo = j * piece, hi = j + 1 == L ? nbytes : (j + 1) * piece;
+                    if ((e = cudaMemcpyAsync(static_cast<char *>(dst) + lo, static_cast<const char *>(src) + lo, hi - lo,
+                                             cudaMemcpyDeviceToDevice, s)) != cudaSuccess)
+                        return fail_cuda(ctx, "cudaMemcpyAsync (staggered first chunk)", e);
+                    if (j + 1 < L && ((e = cudaEventRecord(ctx->chain_ev_part[j], s)) != cudaSuccess ||
+                                      (e = cudaStreamWaitEvent(lanes[j + 1], ctx->chain_ev_part[j], 0)) != cudaSuccess))
+                        return fail_cuda(ctx, "offsetting the chain's lanes", e);
+                }
             } else if ((e = cudaMemcpyAsync(static_cast<char *>(dst) + off, static_cast<const char *>(src) + off, nbytes,
                                             cudaMemcpyDeviceToDevice, s)) != cudaSuccess)
                 return fail_cuda(ctx, "cudaMemcpyAsync", e);
-            if (i > 0 && (e = cudaStreamWaitEvent(s, ctx->chain_ev[(i - 1) & 1u], 0)) != cudaSuccess)
+            if (i > 0 && (e = cudaStreamWaitEvent(s, ctx->chain_ev_pub[(i - 1) % L], 0)) != cudaSuccess)
                 return fail_cuda(ctx, "ordering the chain's publications", e);
             maize::chain_step_kernel<<<1, 32, 0, s>>>(static_cast<uint32_t *>(dst_flag), v, nullptr, 0, ctx->d_status,
                                                       ctx->timeout_ns);
             ctx->launches += 1;
             if ((e = cudaGetLastError()) != cudaSuccess)
                 return fail_cuda(ctx, "kernel launch", e);
-            if ((e = cudaEventRecord(ctx->chain_ev[i & 1u], s)) != cudaSuccess)
+            if ((e = cudaEventRecord(ctx->chain_ev_pub[lane], s)) != cudaSuccess)
                 return fail_cuda(ctx, "cudaEventRecord", e);
         }
         // join: the caller's stream continues after the last publication (which is after all earlier ones)
-        if (((i - 1) & 1u) == 1u && (e = cudaStreamWaitEvent(stream, ctx->chain_ev[1], 0)) != cudaSuccess)
-            return fail_cuda(ctx, "joining the chain's helper stream", e);
+        if ((i - 1) % L != 0 && (e = cudaStreamWaitEvent(stream, ctx->chain_ev_pub[(i - 1) % L], 0)) != cudaSuccess)
+            return fail_cuda(ctx, "joining the chain's helper streams", e);
         return MAIZE_OK;
     }
     // Per chunk: one copy and ONE one-thread kernel that publishes the chunk just copied and, on a rank that

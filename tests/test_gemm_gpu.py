@@ -37,7 +37,7 @@ def test_bounded_wait_returns_timeout(ctx):
 def test_settings_read_back(ctx):
     """Every key of maize_ctx_set can be read with maize_ctx_get (no kernel is launched here)."""
     for key, value in (("group_rows", 1024), ("b_static", 1), ("push_threads", 256), ("max_ctas", 100),
-                       ("force_kernel", 2), ("debug_flags", 0), ("chain_streams", 2), ("repack_bytes", 4096), ("pdl", 0),
+                       ("force_kernel", 2), ("debug_flags", 0), ("chain_streams", 3), ("repack_bytes", 4096), ("pdl", 0),
                        ("serpentine", 0), ("tail_split", 0), ("tma_store", 0), ("tma_promotion", 2)):
         before = ctx.get(key)
         try:

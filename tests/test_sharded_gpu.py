@@ -84,7 +84,7 @@ def test_two_gpu_sharded_gemm(tmp_path, oracle, transport):
     _check(oracle, tmp_path, world, m, n, k, steps, transport)
 
 
-@pytest.mark.parametrize("streams", [1, 2])
+@pytest.mark.parametrize("streams", [1, 2, 4])
 @pytest.mark.parametrize("fused", [False, True])
 @pytest.mark.parametrize("a_event", [False, True])
 def test_chain_variants(tmp_path, oracle, fused, streams, a_event):

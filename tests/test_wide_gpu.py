@@ -45,14 +45,19 @@ def test_wide_tile_is_bit_identical_to_the_pair_kernel(ctx, oracle):
 
 
 def test_wide_tile_is_chosen_when_enabled(ctx, oracle):
-    """With "wide_tile" on (the default), long-K shapes of up to about a millisecond whose rounds of 256 x 512 tiles
-    are nearly full take the wide kernel; others stay with the 256 x 256 pair kernel."""
+    """With "wide_tile" on (the default), long-K shapes whose rounds of 256 x 512 tiles are nearly full take the wide
+    kernel; others stay with the 256 x 256 pair kernel."""
     assert ctx.get("wide_tile") in (0, 1)
     before = ctx.get("wide_tile")
     ctx.set("wide_tile", 1)
     try:
         assert ctx.pick_kernel(8192, 8192, 8192) == "sm100_2cta_256x512x64_s4"
-        assert ctx.pick_kernel(16384, 16384, 16384) == "sm100_2cta_256x256x128_s3"  # beyond the size where it pays
+        assert ctx.pick_kernel(16384, 16384, 16384) == "sm100_2cta_256x512x64_s4"
+        ctx.set("wide_max_gflop", 2200)
+        try:
+            assert ctx.pick_kernel(16384, 16384, 16384) == "sm100_2cta_256x256x128_s3"  # capped by the caller
+        finally:
+            ctx.set("wide_max_gflop", 1000000)
         assert ctx.pick_kernel(4096, 4096, 4096) == "sm100_2cta_256x256x128_s3"   # 128 wide tiles: 1.7 rounds
         assert ctx.pick_kernel(8192, 8192, 512) == "sm100_2cta_256x256x128_s3"    # K too short
         m, n, k = 2048, 4608, 2048  # 8 x 9 = 72 tiles: one round of 74 pairs, nearly full
