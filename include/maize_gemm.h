@@ -283,7 +283,8 @@ MAIZE_API maize_status_t maize_flag_store(maize_ctx_t *ctx, void *flag, uint32_t
  *   b_shards[g] (end - first) x K on device g, dense rows;  c_shards[g]  M x (end - first) on device g, dense rows
  * A is forwarded along the chain root, root+1, ... (index order, wrapping) in chunks of "chunk_rows" rows with
  * device-to-device copies; the root runs one GEMM launch, every other device one gated launch
- * (maize_gemm_bf16_gated).  The call returns when everything is enqueued on the handle's own streams;
+ * (maize_gemm_bf16_gated).  The call returns when everything is enqueued on the handle's own streams (it first
+ * waits, on the host, for the call before the previous one to have finished, so at most two calls are in flight);
  * maize_mgpu_sync waits for all devices and reports a device-side timeout like maize_ctx_poll.  The buffers of a
  * call must stay untouched until then, except that the next call may follow at once: it orders itself after the
  * previous one (a landing buffer is only overwritten after the device that owns it has finished reading it).

@@ -112,6 +112,11 @@ maize_status_t enqueue_step(maize_mgpu *mg, int g)
     cudaError_t e;
     if ((e = cudaSetDevice(rk.device)) != cudaSuccess)
         return rank_fail(rk, MAIZE_ERR_CUDA, std::string("cudaSetDevice: ") + cudaGetErrorString(e));
+    // The host runs at most two steps ahead of this device: the events of this parity were recorded two steps ago
+    // and are about to be re-recorded.  (Deep queues of cross-device waits also measured slower.)
+    if (s.step >= 2 && ((e = cudaEventSynchronize(rk.gemm_done[s.step & 1])) != cudaSuccess ||
+                        (e = cudaEventSynchronize(rk.fwd_done[s.step & 1])) != cudaSuccess))
+        return rank_fail(rk, MAIZE_ERR_CUDA, std::string("waiting for the step before last: ") + cudaGetErrorString(e));
     const uint64_t row_bytes = uint64_t(s.k) * 2;
     const void *a_here = pos == 0 ? s.a_root : s.a_local[g];
     maize_status_t st;
