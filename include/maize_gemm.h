@@ -124,7 +124,8 @@ MAIZE_API maize_status_t maize_gemm_bf16_ld(maize_ctx_t *ctx, const void *a, uin
  * (crates/maize_tile/src/gmem/col_panel.rs:88-124, gmem_tile.rs:416-432, src/main.rs:57).
  * a_cols == b_rows (= K), c is a_rows x b_cols.  Requires b_cols (ldb) % 8 == 0 and a_cols (lda) % 8 == 0,
  * 16-byte aligned A and B; K itself may be any value.  B's tiles are loaded as 64-column boxes and fed
- * to the tensor core as an MN-major operand; nothing is transposed in memory.
+ * to the tensor core as an MN-major operand; nothing is transposed in memory.  Decode shapes (M <= 128) run on
+ * the pair-split kernels with tiles widened to a multiple of 64 columns; the stream-K kernels take N x K only.
  */
 MAIZE_API maize_status_t maize_gemm_bf16_kn(maize_ctx_t *ctx, const void *a, uint32_t a_rows, uint32_t a_cols,
                                             const void *b, uint32_t b_rows, uint32_t b_cols, void *c, uint32_t c_rows,

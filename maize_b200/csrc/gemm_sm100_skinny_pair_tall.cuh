@@ -14,7 +14,9 @@
 
 namespace maize {
 
-template <uint32_t STAGES>
+// B_KN: B is given K x N row-major; the tile's bn columns (a multiple of 64 then) are loaded as bn / 64 boxes of
+// {64 columns, 64 k-rows} and read by the MMA as an MN-major operand.
+template <uint32_t STAGES, bool B_KN = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNumThreads, 1)
 gemm_bf16_sm100_skinny_pair_tall(const __grid_constant__ CUtensorMap tma_x /* A: M x K, box 128 x 64 */,
                                  const __grid_constant__ CUtensorMap tma_w /* B: N x K, box bn x 64 */,
@@ -42,7 +44,8 @@ gemm_bf16_sm100_skinny_pair_tall(const __grid_constant__ CUtensorMap tma_x /* A:
     const uint32_t warp = threadIdx.x >> 5;
     const uint32_t lane = threadIdx.x & 31u;
     const uint32_t cta_rank = ptx::cluster_cta_rank();
-    const uint32_t idesc = ptx::make_instr_desc_bf16(kBlockM, p.bn);
+    const uint32_t idesc = ptx::make_instr_desc_bf16(kBlockM, p.bn, B_KN);
+    constexpr uint32_t kChunkBytes = kBlockK * 128;  // one 64-column chunk of a K x N tile: 64 k-rows x 128 B
     const uint32_t stage_tx = L::kXBytes + p.bn * kBlockK * 2;  // bytes one stage receives
     // this CTA's half of the k-blocks (the first half gets the odd one)
     const uint32_t kb_half = (p.num_kb + 1) / 2;
@@ -59,8 +62,14 @@ gemm_bf16_sm100_skinny_pair_tall(const __grid_constant__ CUtensorMap tma_x /* A:
     auto issue_w = [&](uint32_t kb, uint32_t stage) {  // B tile of one k-block (and the stage's byte count)
         const uint32_t sw = smem_base + stage * L::kStageBytes + L::kXBytes;
         ptx::mbar_arrive_expect_tx(full_bar(stage), stage_tx);
-        ptx::tma_load_2d_hint(sw, &tma_w, full_bar(stage), static_cast<int32_t>(kb * kBlockK),
-                              static_cast<int32_t>(t * p.bn), pol_stream);
+        if constexpr (B_KN) {
+            for (uint32_t j = 0; j < p.bn / 64u; ++j)  // x = column, y = k row
+                ptx::tma_load_2d_hint(sw + j * kChunkBytes, &tma_w, full_bar(stage), static_cast<int32_t>(t * p.bn + 64u * j),
+                                      static_cast<int32_t>(kb * kBlockK), pol_stream);
+        } else {
+            ptx::tma_load_2d_hint(sw, &tma_w, full_bar(stage), static_cast<int32_t>(kb * kBlockK),
+                                  static_cast<int32_t>(t * p.bn), pol_stream);
+        }
     };
     auto issue_x = [&](uint32_t kb, uint32_t stage) {  // the 128-row A tile (rows past M are zero-filled)
         const uint32_t sx = smem_base + stage * L::kStageBytes;
@@ -140,10 +149,12 @@ gemm_bf16_sm100_skinny_pair_tall(const __grid_constant__ CUtensorMap tma_x /* A:
                 ptx::tcgen05_fence_after();
                 const uint32_t sx = smem_base + stage * L::kStageBytes;
                 const uint64_t dx = ptx::make_smem_desc_sw128(sx);               // A tile: the MMA's M side
-                const uint64_t dw = ptx::make_smem_desc_sw128(sx + L::kXBytes);  // B tile: its N side
+                const uint64_t dw = B_KN ? ptx::make_smem_desc_sw128_mn(sx + L::kXBytes, kChunkBytes)
+                                         : ptx::make_smem_desc_sw128(sx + L::kXBytes);  // B tile: its N side
+                constexpr uint32_t kStepW = B_KN ? 128u : 2u;  // +2048 B or +32 B per 16-wide K step
 #pragma unroll
                 for (uint32_t k = 0; k < kBlockK / kUmmaK; ++k)
-                    ptx::mma_bf16_1cta(tmem_base, dx + 2u * k, dw + 2u * k, idesc, (kb != kb_lo || k != 0u) ? 1u : 0u);
+                    ptx::mma_bf16_1cta(tmem_base, dx + 2u * k, dw + kStepW * k, idesc, (kb != kb_lo || k != 0u) ? 1u : 0u);
                 ptx::mma_commit_1cta(empty_bar(stage));
                 if (++stage == STAGES) {
                     stage = 0;

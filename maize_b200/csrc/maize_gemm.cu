@@ -424,8 +424,14 @@ maize_status_t gemm_impl(maize_ctx_t *ctx, const void *a, uint64_t lda, const vo
     if (b_kn) {
         // K x N tiles come in 64-column chunks: the pair kernel or the one-CTA kernels of width >= 64
         if (ctx->force_kernel != 0) {
-            if (vi == 3 || vi >= kFirstSkinny)
+            if (vi == 3 || (vi >= kFirstSkinny && vi != kSkinnyPair && vi != kSkinnyPairTall))
                 return fail(ctx, MAIZE_ERR_UNSUPPORTED, "this kernel variant does not take a K x N matrix B");
+        } else if (vi == kSkinnyPair || vi == kSkinnyPairTall) {
+            // the pair-split decode kernels take a K x N matrix B (their tile widened to a multiple of 64 columns);
+            // the stream-K kernels do not
+            double pair_us = 0, streamk_us = 0;
+            if (skinny_pair_tile(static_cast<uint32_t>(ctx->sm_count), n, k, &pair_us, &streamk_us) == 0)
+                vi = n > 128 ? 0 : (n > 64 ? 1 : 2);
         } else if (vi >= kFirstSkinny && vi != kPairTail && vi != kPairWideTile) {
             vi = n > 128 ? 0 : (n > 64 ? 1 : 2);
         } else if (vi == 3) {
@@ -444,14 +450,17 @@ maize_status_t gemm_impl(maize_ctx_t *ctx, const void *a, uint64_t lda, const vo
         if (m > kv.block_m)
             return fail(ctx, MAIZE_ERR_UNSUPPORTED, "forced skinny kernel takes fewer rows of A than M");
         double pair_us = 0, streamk_us = 0;
-        const uint32_t bn = skinny_pair_tile(static_cast<uint32_t>(ctx->sm_count), n, k, &pair_us, &streamk_us);
+        uint32_t bn = skinny_pair_tile(static_cast<uint32_t>(ctx->sm_count), n, k, &pair_us, &streamk_us);
+        if (b_kn && bn != 0)
+            bn = (bn + 63u) / 64u * 64u;  // K x N tiles come in chunks of 64 columns
         if (bn == 0)
             return fail(ctx, MAIZE_ERR_UNSUPPORTED, "forced pair-split skinny kernel: N needs more than one wave of tiles");
         CUtensorMap tx, tw;
         maize_status_t sst = make_operand_map(ctx, &tx, a, m, k, lda, tall ? 128 : 32);
         if (sst != MAIZE_OK)
             return sst;
-        sst = make_operand_map(ctx, &tw, b, n, k, ldb, bn);
+        sst = b_kn ? make_operand_map(ctx, &tw, b, k, n, ldb, maize::kBlockK)  // boxes of 64 columns x 64 k-rows
+                   : make_operand_map(ctx, &tw, b, n, k, ldb, bn);
         if (sst != MAIZE_OK)
             return sst;
         maize::SkinnyPairParams pp;
@@ -471,13 +480,15 @@ maize_status_t gemm_impl(maize_ctx_t *ctx, const void *a, uint64_t lda, const vo
         pp.bn = bn;
         pp.tiles_n = (n + bn - 1) / bn;
         pp.num_kb = (k + maize::kBlockK - 1) / maize::kBlockK;
-        auto kernel = tall ? maize::gemm_bf16_sm100_skinny_pair_tall<4> : maize::gemm_bf16_sm100_skinny_pair<4>;
-        if (!ctx->attr_set[vi]) {
+        auto kernel = tall ? (b_kn ? maize::gemm_bf16_sm100_skinny_pair_tall<4, true> : maize::gemm_bf16_sm100_skinny_pair_tall<4, false>)
+                           : (b_kn ? maize::gemm_bf16_sm100_skinny_pair<4, true> : maize::gemm_bf16_sm100_skinny_pair<4, false>);
+        bool &attr_done = b_kn ? ctx->attr_set_kn[vi] : ctx->attr_set[vi];
+        if (!attr_done) {
             cudaError_t ea = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                   maize::SkinnySmemLayout<4>::kDynamicBytes);
             if (ea != cudaSuccess)
                 return fail_cuda(ctx, "cudaFuncSetAttribute(max dynamic smem)", ea);
-            ctx->attr_set[vi] = true;
+            attr_done = true;
         }
         pp.pdl = ctx->pdl;
         pp.b_static = ctx->b_static;

@@ -305,6 +305,30 @@ def test_b_stored_k_by_n(ctx, oracle, m, n, k, force):
                   f"K x N B, {m}x{n}x{k}, kernel {force}")
 
 
+@pytest.mark.parametrize("force,m", [(9, 16), (9, 32), (9, 1), (11, 128), (11, 33), (11, 16), (0, 16), (0, 100)])
+@pytest.mark.parametrize("n,k", [(16384, 4096), (4096, 1024), (1000, 520), (9472, 64), (8200, 264)])
+def test_decode_shapes_with_b_stored_k_by_n(ctx, oracle, force, m, n, k):
+    """The pair-split decode kernels with B given K x N: tiles widened to a multiple of 64 columns, loaded as
+    64-column boxes, MN-major MMA operand; ragged N and K, single and odd k-block counts."""
+    import torch
+    a = oracle.fill_bf16(44, 0, (m, k))
+    b_nk = oracle.fill_bf16(44, 1, (n, k), scale=0.05)
+    ref = oracle.gemm_bf16(a, b_nk)
+    da = to_device(a)
+    db_kn = to_device(np.ascontiguousarray(b_nk.T))  # K x N
+    dc = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+    if force == 0:
+        assert "skinny_pair" in ctx.pick_kernel(m, n, k)
+    ctx.set("force_kernel", force)
+    try:
+        ctx.gemm_kn(da, db_kn, out=dc)
+        ctx.poll()
+    finally:
+        ctx.set("force_kernel", 0)
+    assert_parity(oracle, to_host(dc), ref, k, oracle.max_abs_bf16(a), oracle.max_abs_bf16(b_nk),
+                  f"decode, K x N B, {m}x{n}x{k}, kernel {force}")
+
+
 def test_b_k_by_n_full_config(ctx, oracle):
     """Config c1 (4096^3, the reference demo's own size) with B in the demo's K x N layout."""
     m = n = k = 4096
