@@ -365,7 +365,7 @@ def brief_workload(ctx, name: str, dev, peaks, sampler, reps: int, b_static: boo
         ctx.poll()
     finally:
         ctx.set("b_static", 0)
-    out = {"workload": f"{name}: {desc}", "kernel": ctx.pick_kernel(m, n, k), "ms": ms,
+    out = {"workload": f"{name}: {desc}", "kernel": ctx.last_kernel or ctx.pick_kernel(m, n, k), "ms": ms,
            "launch": "library defaults, B declared static (weights)" if b_static else "library defaults",
            "clocks": sampler.summary(w0, w1) if sampler else None}
     if name == "c3":
@@ -551,7 +551,7 @@ def main():
     repeat_ms, rw0, rw1 = time_loop(kernel_only, reps)
     repeat = {"ms": repeat_ms, "reps": reps, "clocks": sampler.summary(rw0, rw1) if sampler else None}
     kernel_ms = ms_per_step if world == 1 else repeat_ms
-    kernel_name = ctx.pick_kernel(m, ns, k)
+    kernel_name = ctx.last_kernel or ctx.pick_kernel(m, ns, k)   # what the kernel-only loop just launched
 
     # ---- cuBLAS through torch.matmul on the same tensors, interleaved with this library's launches (N = 1)
     cublas = None

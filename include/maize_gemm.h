@@ -171,8 +171,8 @@ MAIZE_API maize_status_t maize_ctx_poll(maize_ctx_t *ctx, void *cuda_stream);
  * of 256 x 256 tiles would leave CTA pairs idle, its tiles are split along K over them), "tma_store"
  * (default 1: the CTA-pair kernels write C through shared memory and TMA stores when C's rows are 16-byte
  * aligned), "c_evict_first" (default 1: those stores carry an evict-first L2 hint, C passes through L2 once),
- * "wide_tile" (default 1: GEMMs with long K and nearly full rounds of tiles use a 256 x 512 tile per CTA
- * pair, which moves a quarter less data from L2 per flop; "wide_max_gflop", default 1000000, is the largest
+ * "wide_tile" (default 1: GEMMs with long K, rounds of tiles at least 86 % full and 16-byte aligned rows of
+ * C use a 256 x 512 tile per CTA pair, which moves a quarter less data from L2 per flop; "wide_max_gflop", default 1000000, is the largest
  * 2MNK / 1e9 that takes it: multi-millisecond GEMMs run back to back for seconds are 1-3 % faster on the 256 x 256
  * tile), "tma_promotion" (L2 promotion of the operand tensor maps: 0 none, 1 64 B, 2 128 B, 3 256 B
  * = default), "chain_streams"
@@ -186,11 +186,14 @@ MAIZE_API maize_status_t maize_ctx_poll(maize_ctx_t *ctx, void *cuda_stream);
 /* An environment variable MAIZE_<KEY> (upper case, e.g. MAIZE_PDL=0, MAIZE_TMA_STORE=0) presets that tunable in
  * every context created afterwards; maize_ctx_set still overrides it. */
 MAIZE_API maize_status_t maize_ctx_set(maize_ctx_t *ctx, const char *key, int64_t value);
-/* Reads back any key of maize_ctx_set, plus "sm_count" and "device". */
+/* Reads back any key of maize_ctx_set, plus "sm_count", "device" and "last_kernel" (id, as maize_kernel_name
+ * takes it, of the GEMM kernel the context's last call launched; 0 before the first). */
 MAIZE_API maize_status_t maize_ctx_get(const maize_ctx_t *ctx, const char *key, int64_t *value);
 
 /* Name of kernel variant `id` (1-based), NULL past the end; id of the variant the
- * heuristic picks for a shape. */
+ * heuristic picks for a shape of densely stored, aligned operands.  A call may still run another one: a K x N
+ * matrix B, a gated launch, or rows of C that TMA cannot store keep the 256 x 256 tile where the shape alone would
+ * take the 256 x 512 one ("last_kernel" tells). */
 MAIZE_API const char *maize_kernel_name(int id);
 MAIZE_API int maize_pick_kernel(const maize_ctx_t *ctx, uint32_t m, uint32_t n, uint32_t k);
 

@@ -104,6 +104,7 @@ struct maize_ctx {
     DeviceStatus *h_status = nullptr;  // pinned
     uint64_t timeout_ns = 2000000000ull;
     int force_kernel = 0;
+    int last_kernel = 0;             // public id of the GEMM kernel the last call launched
     int max_ctas = 0;
     uint32_t debug_flags = 0;
     uint32_t group_rows = 2048;
@@ -276,7 +277,7 @@ uint32_t skinny_pair_tile(uint32_t sms, uint32_t n, uint32_t k, double *est_pair
 // Whether the 256 x 512 pair tile suits a shape: K long enough that the exposed part of its epilogue is small,
 // little of the last column block wasted, and whole rounds of tiles nearly full (it has no K split for a partial
 // last round).
-bool wide_tile_suits(uint32_t sms, uint32_t m, uint32_t n, uint32_t k, uint64_t max_gflop)
+bool wide_tile_suits(uint32_t sms, uint32_t m, uint32_t n, uint32_t k, uint64_t max_gflop, double min_fill = 0.86)
 {
     const uint64_t pairs = sms / 2 ? sms / 2 : 1;
     if (k < 2048 || m <= 128 || n < 512)
@@ -292,7 +293,9 @@ bool wide_tile_suits(uint32_t sms, uint32_t m, uint32_t n, uint32_t k, uint64_t 
         return false;
     const uint64_t tiles = ((uint64_t(m) + 255) / 256) * (cols / 512);
     const uint64_t rounds = (tiles + pairs - 1) / pairs;
-    return double(tiles) >= 0.92 * double(rounds * pairs);
+    // 0.865 (4096^3: 128 tiles in two rounds; 16384 x 2048 x 16384: 256 tiles in four) measured 3 % and 1 % ahead of
+    // the 256 x 256 kernel with its K-split last round, 0.757 (8192 x 3584 x 8192) 1.5 % behind
+    return double(tiles) >= min_fill * double(rounds * pairs);
 }
 
 int pick_variant(const maize_ctx_t *ctx, uint32_t m, uint32_t n, uint32_t k)
@@ -420,6 +423,11 @@ maize_status_t gemm_impl(maize_ctx_t *ctx, const void *a, uint64_t lda, const vo
         // only the tiled kernels watch the gate; a forced or chosen decode kernel is replaced
         if (vi >= kFirstSkinny && vi != kPairTail && vi != kPairWideTile)
             vi = n > 128 ? 0 : (n > 64 ? 1 : (n > 32 ? 2 : 3));
+        // rows that land last are multiplied last, and a partial last round of wide tiles would leave twice the
+        // work behind the last chunk: a gated launch takes the wide tile only when its rounds are nearly full
+        if (vi == kPairWideTile && ctx->force_kernel == 0 &&
+            !wide_tile_suits(static_cast<uint32_t>(ctx->sm_count), m, n, k, ctx->wide_max_gflop, 0.92))
+            vi = kPairWide;
     }
     if (b_kn) {
         // K x N tiles come in 64-column chunks: the pair kernel or the one-CTA kernels of width >= 64
@@ -443,7 +451,13 @@ maize_status_t gemm_impl(maize_ctx_t *ctx, const void *a, uint64_t lda, const vo
             return fail(ctx, MAIZE_ERR_UNSUPPORTED, "the 256 x 512 pair kernel does not take a K x N matrix B");
         vi = kPairWide;
     }
+    // The wide tile's epilogue is not hidden behind the next tile's main loop, so it has to be the fast one: rows
+    // of C that TMA can store.  (4111 x 3967 x 4104, odd row pitch of C: 0.164 ms against 0.137 ms.)
+    if (vi == kPairWideTile && ctx->force_kernel == 0 &&
+        !(ctx->tma_store && ldc % 8 == 0 && reinterpret_cast<uintptr_t>(c) % 16 == 0))
+        vi = kPairWide;
     const KernelVariant &kv = kVariants[vi];
+    ctx->last_kernel = vi + 1;
 
     if (vi == kSkinnyPair || vi == kSkinnyPairTall) {
         const bool tall = vi == kSkinnyPairTall;
@@ -1225,6 +1239,8 @@ maize_status_t maize_ctx_get(const maize_ctx_t *ctx, const char *key, int64_t *v
         *value = ctx->tma_promotion;
     else if (!strcmp(key, "repack_bytes"))
         *value = static_cast<int64_t>(ctx->repack_bytes);
+    else if (!strcmp(key, "last_kernel"))
+        *value = ctx->last_kernel;
     else
         return MAIZE_ERR_INVALID_ARG;
     return MAIZE_OK;

@@ -103,6 +103,12 @@ class Context:
     def pick_kernel(self, m: int, n: int, k: int) -> str:
         return self._lib.maize_kernel_name(self._lib.maize_pick_kernel(self._h, m, n, k)).decode()
 
+    @property
+    def last_kernel(self) -> str:
+        """Name of the GEMM kernel the last call on this context launched ("" before the first)."""
+        kid = self.get("last_kernel")
+        return self._lib.maize_kernel_name(kid).decode() if kid > 0 else ""
+
     def poll(self, stream=None) -> None:
         """Synchronise the stream and raise if a device wait timed out."""
         self._check(self._lib.maize_ctx_poll(self._h, _stream_handle(stream)))

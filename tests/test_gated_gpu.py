@@ -24,7 +24,7 @@ def _plain_and_inputs(ctx, oracle, m, n, k, seed, force):
     return a, b, da, db, want
 
 
-@pytest.mark.parametrize("force", [0, 1, 2, 3, 4, 5])
+@pytest.mark.parametrize("force", [0, 1, 2, 3, 4, 5, 10, 12])
 @pytest.mark.parametrize("m,n,k,rows", [(300, 520, 264, 128), (1500, 1300, 520, 256), (2048, 4096, 512, 1024)])
 def test_preset_count_is_bit_identical(ctx, oracle, m, n, k, rows, force):
     """With every chunk already counted the gated call is the plain call, on each tiled kernel; the count may
@@ -45,7 +45,7 @@ def test_preset_count_is_bit_identical(ctx, oracle, m, n, k, rows, force):
     assert_parity(oracle, to_host(want), ref, k, oracle.max_abs_bf16(a), oracle.max_abs_bf16(b), "gated, preset")
 
 
-@pytest.mark.parametrize("force", [0, 1, 5])
+@pytest.mark.parametrize("force", [0, 1, 5, 10, 12])
 def test_host_raises_the_count_while_the_kernel_runs(ctx, oracle, force):
     """Nothing has landed at launch; the host counts the chunks in mapped pinned memory, a few at a time, and the
     kernel's loaders follow.  The result is bit-identical to the plain call."""
@@ -75,7 +75,7 @@ def test_host_raises_the_count_while_the_kernel_runs(ctx, oracle, force):
         ctx.set("force_kernel", 0)
 
 
-@pytest.mark.parametrize("force", [1, 5])
+@pytest.mark.parametrize("force", [1, 5, 12])
 def test_count_that_never_comes_times_out(ctx, oracle, force):
     """Half of A is counted and the rest never is: the kernel ends by itself after the budget, the status says
     timeout, and the next call on the same context is correct."""

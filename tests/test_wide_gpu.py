@@ -58,7 +58,8 @@ def test_wide_tile_is_chosen_when_enabled(ctx, oracle):
             assert ctx.pick_kernel(16384, 16384, 16384) == "sm100_2cta_256x256x128_s3"  # capped by the caller
         finally:
             ctx.set("wide_max_gflop", 1000000)
-        assert ctx.pick_kernel(4096, 4096, 4096) == "sm100_2cta_256x256x128_s3"   # 128 wide tiles: 1.7 rounds
+        assert ctx.pick_kernel(4096, 4096, 4096) == "sm100_2cta_256x512x64_s4"    # 128 wide tiles: two rounds, 86 % full
+        assert ctx.pick_kernel(8192, 3584, 8192) == "sm100_2cta_256x256x128_s3"   # 224 wide tiles: four rounds, 76 % full
         assert ctx.pick_kernel(8192, 8192, 512) == "sm100_2cta_256x256x128_s3"    # K too short
         m, n, k = 2048, 4608, 2048  # 8 x 9 = 72 tiles: one round of 74 pairs, nearly full
         assert ctx.pick_kernel(m, n, k) == "sm100_2cta_256x512x64_s4"
@@ -87,3 +88,24 @@ def test_wide_tile_canaries(ctx, oracle):
     assert np.all(body[:, n:] == seven)
     assert_parity(oracle, np.ascontiguousarray(body[:, :n]), oracle.gemm_bf16(a, b), k, oracle.max_abs_bf16(a),
                   oracle.max_abs_bf16(b), "wide tile, strided C")
+
+
+def test_wide_tile_needs_rows_of_c_that_tma_can_store(ctx, oracle):
+    """The wide tile's epilogue is exposed, so the heuristic takes it only when C leaves through TMA stores: the
+    same shape with an odd row pitch of C runs on the 256 x 256 pair kernel ("last_kernel" tells which ran)."""
+    import torch
+    m, n, k = 2048, 4608, 2048
+    a = oracle.fill_bf16(75, 0, (m, k))
+    b = oracle.fill_bf16(75, 1, (n, k))
+    ref = oracle.gemm_bf16(a, b)
+    da, db = to_device(a), to_device(b)
+    dense = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+    ctx.gemm(da, db, out=dense)
+    assert ctx.last_kernel == "sm100_2cta_256x512x64_s4"
+    wide = torch.full((m, n + 3), float("nan"), dtype=torch.bfloat16, device="cuda")
+    ctx.gemm(da, db, out=wide[:, :n])
+    assert ctx.last_kernel == "sm100_2cta_256x256x128_s3"
+    ctx.poll()
+    assert torch.equal(dense.view(torch.int16), wide[:, :n].view(torch.int16))
+    assert torch.isnan(wide[:, n:]).all()
+    assert_parity(oracle, to_host(dense), ref, k, oracle.max_abs_bf16(a), oracle.max_abs_bf16(b), "wide tile, dense C")
