@@ -50,7 +50,7 @@ SPEC_TFLOPS, SPEC_HBM_GBS = 2250.0, 8000.0
 # DRAM bytes per launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum of one ncu
 # capture on a B200; the summaries with the commands are under profiles/).  None where not captured.
 NCU_TRAFFIC = {
-    "c4": (13.6e9, "profiles/gemm_pair_16384.md (other captures of the same launch: 9.3 to 18 GB)"),
+    "c4": (11.17e9, "profiles/gemm_pair_16384.md, the 256 x 512 tile with 4096-row groups (captures of the 256 x 256 kernel on the same workload: 9.3 to 18 GB)"),
     "t": (0.95e9, "profiles/gemm_wide_8192.md"),
     "c3": (1.376e8, "profiles/skinny_16x16384x4096.md"),
 }

@@ -158,7 +158,7 @@ MAIZE_API maize_status_t maize_ctx_poll(maize_ctx_t *ctx, void *cuda_stream);
 /* Tunables.  Keys: "timeout_ns" (device wait budget), "force_kernel" (0 = heuristic,
  * see maize_kernel_name), "max_ctas" (cap on the persistent grid, 0 = SM count),
  * "profile" (1 = per-CTA cycle accounting, see maize_ctx_read_profile), "group_rows" (rows of A
- * whose tiles are scheduled together, default 2048), "push_threads" (threads per CTA of the copy
+ * whose tiles are scheduled together; default 0 = by kernel: 2048, and 4096 for the 256 x 512 tile), "push_threads" (threads per CTA of the copy
  * kernels of the multi-GPU path, default 512), "pdl" (default 1: the GEMM kernels are launched with
  * programmatic stream serialization, so that a kernel's set-up (barriers, tensor memory, descriptor
  * prefetch) runs while the stream's previous kernel drains; the kernel waits for that kernel to complete
