@@ -49,6 +49,8 @@ L2_BYTES = 126 * 1024 * 1024
 SPEC_TFLOPS, SPEC_HBM_GBS = 2250.0, 8000.0
 # DRAM bytes per launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum of one ncu
 # capture on a B200; the summaries with the commands are under profiles/).  None where not captured.
+SETTLE_S = 1.0   # idle before each of the brief workloads (see brief_workload)
+
 NCU_TRAFFIC = {
     "c4": (11.17e9, "profiles/gemm_pair_16384.md, the 256 x 512 tile with 4096-row groups (captures of the 256 x 256 kernel on the same workload: 9.3 to 18 GB)"),
     "t": (0.95e9, "profiles/gemm_wide_8192.md"),
@@ -354,6 +356,11 @@ def brief_workload(ctx, name: str, dev, peaks, sampler, reps: int, b_static: boo
     sets = [(draw((m, k), sa, dname, dev, gen), draw((n, k), sb, dname, dev, gen),
              torch.empty((m, n), dtype=torch.bfloat16, device=dev)) for _ in range(n_sets)]
     ctx.set("b_static", 1 if b_static else 0)
+    # The loops before this one leave the part at the low clock its power controller chose for them (1.2 GHz after
+    # seconds of 16384^3), and that clock lasts longer than a short workload's whole loop: idle first, so that every
+    # workload is measured from the same state (the idle is outside every timed region and is reported).
+    torch.cuda.synchronize()
+    time.sleep(SETTLE_S)
     try:
         def ours(i):
             a, b, c = sets[i % n_sets]
@@ -366,6 +373,7 @@ def brief_workload(ctx, name: str, dev, peaks, sampler, reps: int, b_static: boo
     finally:
         ctx.set("b_static", 0)
     out = {"workload": f"{name}: {desc}", "kernel": ctx.last_kernel or ctx.pick_kernel(m, n, k), "ms": ms,
+           "idle_before_s": SETTLE_S,
            "launch": "library defaults, B declared static (weights)" if b_static else "library defaults",
            "clocks": sampler.summary(w0, w1) if sampler else None}
     if name == "c3":
@@ -378,6 +386,8 @@ def brief_workload(ctx, name: str, dev, peaks, sampler, reps: int, b_static: boo
                                                        "peak": peaks["bf16_tflops"], "frac_of_spec_2250": tf / SPEC_TFLOPS})
     if cublas:
         c2 = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
+        torch.cuda.synchronize()
+        time.sleep(SETTLE_S)
 
         def lib(i):
             a, b, _ = sets[i % n_sets]
