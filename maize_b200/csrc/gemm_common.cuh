@@ -271,16 +271,36 @@ __global__ void __launch_bounds__(256) repack_rows_kernel(RepackSegment s0, Repa
     // a GEMM launched behind this copy with programmatic stream serialization may do its set-up meanwhile (it
     // waits for this grid to complete before it loads anything)
     ptx::grid_dependency_launch_dependents();
-    // blockIdx.y strides over the rows of both segments, x over the 16-byte columns of a row
-    const uint32_t total = s0.rows + s1.rows;
-    for (uint32_t r = blockIdx.y; r < total; r += gridDim.y) {
+    // The 16-byte pieces of both segments form one index space that the grid strides over, four loads in flight
+    // per thread: a few CTAs per SM with work for all their lanes, instead of a CTA per 4 KiB of a row.
+    const uint64_t total = static_cast<uint64_t>(s0.rows + s1.rows) * cols16;
+    const uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
+    auto locate = [&](uint64_t idx, const uint4 *&src, uint4 *&dst) {
+        const uint32_t r = static_cast<uint32_t>(idx / cols16);
+        const uint32_t c = static_cast<uint32_t>(idx - static_cast<uint64_t>(r) * cols16);
         const bool first = r < s0.rows;
         const RepackSegment &g = first ? s0 : s1;
         const uint32_t row = first ? r : r - s0.rows;
-        const uint4 *s = g.src + static_cast<uint64_t>(row) * g.src_pitch16;
-        uint4 *d = g.dst + static_cast<uint64_t>(row) * g.dst_pitch16;
-        for (uint32_t c = blockIdx.x * blockDim.x + threadIdx.x; c < cols16; c += gridDim.x * blockDim.x)
-            d[c] = s[c];
+        src = g.src + static_cast<uint64_t>(row) * g.src_pitch16 + c;
+        dst = g.dst + static_cast<uint64_t>(row) * g.dst_pitch16 + c;
+    };
+    for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += 4 * stride) {
+        uint4 v[4];
+        uint4 *d[4];
+#pragma unroll
+        for (uint32_t u = 0; u < 4; ++u) {
+            const uint64_t idx = i + u * stride;
+            d[u] = nullptr;
+            if (idx < total) {
+                const uint4 *s;
+                locate(idx, s, d[u]);
+                v[u] = __ldg(s);
+            }
+        }
+#pragma unroll
+        for (uint32_t u = 0; u < 4; ++u)
+            if (d[u])
+                *d[u] = v[u];
     }
 }
 

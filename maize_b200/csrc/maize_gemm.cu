@@ -601,9 +601,10 @@ maize_status_t gemm_impl(maize_ctx_t *ctx, const void *a, uint64_t lda, const vo
                 lda = pitch;
             }
             if (nseg > 0) {
-                const uint32_t rows = seg[0].rows + seg[1].rows;
-                const uint32_t gx = (k / 8 + 255) / 256 < 4 ? (k / 8 + 255) / 256 : 4;
-                const dim3 rgrid(gx ? gx : 1, rows < 65535u ? rows : 65535u);
+                const uint64_t pieces = uint64_t(seg[0].rows + seg[1].rows) * (k / 8);  // 16 bytes each
+                const uint64_t want = (pieces + 1023) / 1024;                          // four per thread
+                const uint64_t cap = uint64_t(ctx->sm_count) * 8;
+                const uint32_t rgrid = static_cast<uint32_t>(want < cap ? (want ? want : 1) : cap);
                 maize::repack_rows_kernel<<<rgrid, 256, 0, stream>>>(seg[0], seg[1], k / 8);
                 ctx->launches += 1;
                 cudaError_t er = cudaGetLastError();
