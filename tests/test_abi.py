@@ -145,3 +145,16 @@ def test_rust_binding_in_the_integration_notes_matches_the_header():
             if "*" not in c_arg:
                 width = {"uint32_t": "u32", "uint64_t": "u64", "int": "c_int", "int64_t": "i64"}[c_arg.split()[0]]
                 assert r_type == width, (name, c_arg, r_arg)
+
+
+def test_every_tunable_is_documented_in_the_header():
+    """Every key that maize_ctx_set / maize_ctx_get / maize_mgpu_set accept appears, quoted, in the header's text."""
+    root = Path(__file__).resolve().parent.parent
+    header = (root / "include" / "maize_gemm.h").read_text()
+    keys = set()
+    for name in ("maize_gemm.cu", "maize_mgpu.cu"):
+        src = (root / "maize_b200" / "csrc" / name).read_text()
+        keys |= set(re.findall(r'strcmp\(key, "([a-z_0-9]+)"\)', src))
+    assert len(keys) >= 20
+    missing = sorted(k for k in keys if f'"{k}"' not in header)
+    assert not missing, missing
