@@ -343,7 +343,8 @@ def draw(shape, sigma, dname, dev, gen):
     return (torch.randn(shape, device=dev, generator=gen) * sigma).to(torch.bfloat16)
 
 
-def brief_workload(ctx, name: str, dev, peaks, sampler, reps: int, b_static: bool = False, cublas: bool = True):
+def brief_workload(ctx, name: str, dev, peaks, sampler, reps: int, b_static: bool = False, cublas: bool = True,
+                   kn: bool = False):
     """One of the other workloads on one GPU: warm up, time `reps` launches (rotating over input sets when the
     inputs fit in L2), the same with torch.matmul, and check sampled rows against the CPU oracle."""
     import torch
@@ -355,6 +356,8 @@ def brief_workload(ctx, name: str, dev, peaks, sampler, reps: int, b_static: boo
     n_sets = max(1, -(-4 * L2_BYTES // nbytes)) if nbytes < 2 * L2_BYTES else 1
     sets = [(draw((m, k), sa, dname, dev, gen), draw((n, k), sb, dname, dev, gen),
              torch.empty((m, n), dtype=torch.bfloat16, device=dev)) for _ in range(n_sets)]
+    # kn: the same B handed over as K x N row-major (the reference demo's layout), through maize_gemm_bf16_kn
+    sets_kn = [b.t().contiguous() for _, b, _ in sets] if kn else None
     ctx.set("b_static", 1 if b_static else 0)
     # The loops before this one leave the part at the low clock its power controller chose for them (1.2 GHz after
     # seconds of 16384^3), and that clock lasts longer than a short workload's whole loop: idle first, so that every
@@ -364,7 +367,10 @@ def brief_workload(ctx, name: str, dev, peaks, sampler, reps: int, b_static: boo
     try:
         def ours(i):
             a, b, c = sets[i % n_sets]
-            ctx.gemm(a, b, out=c)
+            if kn:
+                ctx.gemm_kn(a, sets_kn[i % n_sets], out=c)
+            else:
+                ctx.gemm(a, b, out=c)
         for i in range(3):
             ours(i)
         total = max(reps, 3) * n_sets if n_sets > 1 else max(reps, 3)
@@ -374,7 +380,8 @@ def brief_workload(ctx, name: str, dev, peaks, sampler, reps: int, b_static: boo
         ctx.set("b_static", 0)
     out = {"workload": f"{name}: {desc}", "kernel": ctx.last_kernel or ctx.pick_kernel(m, n, k), "ms": ms,
            "idle_before_s": SETTLE_S,
-           "launch": "library defaults, B declared static (weights)" if b_static else "library defaults",
+           "launch": "library defaults, B declared static (weights)" if b_static else
+                     ("library defaults, B stored K x N" if kn else "library defaults"),
            "clocks": sampler.summary(w0, w1) if sampler else None}
     if name == "c3":
         gbs = nbytes / (ms * 1e-3) / 1e9
@@ -391,7 +398,10 @@ def brief_workload(ctx, name: str, dev, peaks, sampler, reps: int, b_static: boo
 
         def lib(i):
             a, b, _ = sets[i % n_sets]
-            torch.matmul(a, b.t(), out=c2)
+            if kn:
+                torch.matmul(a, sets_kn[i % n_sets], out=c2)
+            else:
+                torch.matmul(a, b.t(), out=c2)
         for i in range(3):
             lib(i)
         ms_lib, _, _ = time_loop(lib, total)
@@ -403,7 +413,7 @@ def brief_workload(ctx, name: str, dev, peaks, sampler, reps: int, b_static: boo
     idx = torch.from_numpy(rows).to(dev)
     ok, err, bound = check_rows(to_u16(a[idx]), to_u16(b), to_u16(c[idx]), k, oracle.host_cores())
     out["verified"] = {"rows": int(len(rows)), "max_err": err, "bound": bound, "ok": ok}
-    del sets, a, b, c
+    del sets, sets_kn, a, b, c
     torch.cuda.empty_cache()
     return out
 
@@ -589,10 +599,11 @@ def main():
         del c_lib
     if world == 1 and not args.no_others and args.workload == "c4" and not kn:
         others = []
-        for name, static in (("c1", False), ("c2", False), ("c3", False), ("c3", True), ("c5", False), ("t", False)):
+        for name, static, b_kn in (("c1", False, False), ("c2", False, False), ("c3", False, False), ("c3", True, False),
+                                   ("c3", False, True), ("c5", False, False), ("t", False, False)):
             try:
                 others.append(brief_workload(ctx, name, dev, peaks, sampler, reps=max(args.steps, 5), b_static=static,
-                                             cublas=not static))
+                                             cublas=not static, kn=b_kn))
             except Exception as exc:  # report, never hide
                 others.append({"workload": name, "error": repr(exc)})
 
